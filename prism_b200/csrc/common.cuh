@@ -1,0 +1,99 @@
+// Shared device helpers for the prism_b200 kernels (sm_100a).
+//
+// Conventions used by every kernel in this directory:
+//  * activations are float or __nv_bfloat16 (template parameter T); all
+//    arithmetic is float, with one rounding where a tensor is stored;
+//  * one-dimensional parameters (norm weights, biases) and the embedding
+//    table keep the dtype they have in the model file; a kernel receives
+//    them as `const void*` plus a flag (`PARAM_F32` / `PARAM_BF16`);
+//  * a kernel that meets an index it must not follow (token id outside the
+//    vocabulary, page id outside the pool) records a code in the device
+//    error word and skips the access instead of faulting;
+//  * launchers are `extern "C"`, take raw device pointers and a stream, and
+//    return the cudaError_t of the launch as an int.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define PRISM_DTYPE_F32 0
+#define PRISM_DTYPE_BF16 1
+
+// error codes written to the device error word (first one wins)
+#define PRISM_ERR_TOKEN_RANGE 1
+#define PRISM_ERR_PAGE_RANGE 2
+#define PRISM_ERR_POSITION_RANGE 3
+#define PRISM_ERR_WAIT_TIMEOUT 4
+
+#define PRISM_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace prism {
+
+__device__ __forceinline__ void report_error(int* err, int code) {
+    if (err != nullptr) atomicCAS(err, 0, code);
+}
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+// element i of a parameter vector stored as float or bf16
+__device__ __forceinline__ float load_param(const void* p, int is_bf16, size_t i) {
+    return is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
+                   : reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` is 33 floats of shared memory.  The order of additions depends
+// only on the block size, never on the data or the grid.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+}  // namespace prism

@@ -1,0 +1,65 @@
+// Residual add fused with RMSNorm.
+//
+//   residual[r, :] += sum_s delta[s, r, :]          (float32, in place)
+//   out[i, :] = residual[r, :] * rsqrt(mean(residual[r, :]^2) + eps) * w
+//
+// which is andre-fu/prism's `residual + F.linear(...)` followed by
+// `fused_rms_norm` (engine/executor.py:122-124; formula
+// engine/fused_kernels.py:41-49), with the sum and the norm in float32 and a
+// single rounding at the store of `out`.  `rows` (optional) lists the rows to
+// process, so that the final norm touches only the rows whose logits are
+// wanted (executor.py:130).  One block per row; the order of additions is
+// fixed by the block size, so a row's result does not depend on the batch.
+#include "common.cuh"
+
+namespace prism {
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                   int nsplit, size_t split_stride,
+                                   const void* __restrict__ weight, int weight_bf16, float eps,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int H) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* res = residual + (size_t)r * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = res[c];
+        if (delta != nullptr) {
+            for (int s = 0; s < nsplit; ++s)
+                v += to_float(delta[(size_t)s * split_stride + (size_t)r * H + c]);
+            res[c] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)i * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        o[c] = from_float<TO>(res[c] * inv * load_param(weight, weight_bf16, c));
+}
+
+}  // namespace prism
+
+// delta_dtype / out_dtype: PRISM_DTYPE_*.  delta may be null (plain norm).
+PRISM_EXPORT int prism_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int nsplit,
+                                   long long split_stride, const void* weight, int weight_dtype,
+                                   float eps, void* out, int out_dtype, const int* rows, int nrows,
+                                   int H, cudaStream_t stream) {
+    if (nrows <= 0) return 0;
+    const int threads = H >= 2048 ? 256 : (H >= 512 ? 128 : 64);
+    const int wb = weight_dtype == PRISM_DTYPE_BF16;
+#define LAUNCH(TD, TO)                                                                          \
+    prism::add_rmsnorm_kernel<TD, TO><<<nrows, threads, 0, stream>>>(                             \
+        residual, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)out, rows, H)
+    if (delta_dtype == PRISM_DTYPE_BF16) {
+        if (out_dtype == PRISM_DTYPE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else LAUNCH(__nv_bfloat16, float);
+    } else {
+        if (out_dtype == PRISM_DTYPE_BF16) LAUNCH(float, __nv_bfloat16);
+        else LAUNCH(float, float);
+    }
+#undef LAUNCH
+    return (int)cudaPeekAtLastError();
+}

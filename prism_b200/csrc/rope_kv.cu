@@ -1,0 +1,106 @@
+// Rotary position encoding of q and k fused with the store of k and v into
+// the paged cache.
+//
+// Rotation (andre-fu/prism engine/executor.py:18-21,48-57,117-118): pairs
+// (j, j + rd/2) of the first `rd` dims of a head,
+//     x1' = x1*cos(a) - x2*sin(a),  x2' = x2*cos(a) + x1*sin(a),
+//     a = position * inv_freq[j]
+// with the angle, cos and sin in float32 (no rounded table).  q is rotated in
+// place; k is rotated and written, with v unrotated, to slot `position` of
+// the request's pages: page = block_table[seg, position / P], offset
+// position % P (the append that flash_attn_with_kvcache does at
+// executor.py:119-120).  Cache layout: [page, P, nkv, hd].
+#include "common.cuh"
+
+namespace prism {
+
+template <typename T>
+__global__ void rope_kv_kernel(T* __restrict__ q, T* __restrict__ k, const T* __restrict__ v,
+                               int row_stride, const int* __restrict__ positions,
+                               const int* __restrict__ tok_seg, const float* __restrict__ inv_freq,
+                               int rd, T* __restrict__ kc, T* __restrict__ vc,
+                               const int* __restrict__ block_table, int bt_width, int page_size,
+                               int num_pages, int nh, int nkv, int hd, int max_pos, int* err) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0) report_error(err, PRISM_ERR_POSITION_RANGE);
+        return;
+    }
+    T* qrow = q + (size_t)t * row_stride;
+    T* krow = k + (size_t)t * row_stride;
+    const T* vrow = v + (size_t)t * row_stride;
+
+    size_t slot = 0;
+    bool store = kc != nullptr;
+    if (store) {
+        const int page = block_table[(size_t)tok_seg[t] * bt_width + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
+            store = false;
+        } else {
+            slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
+        }
+    }
+    const int half = rd / 2;
+    const int pairs_per_head = hd - half;   // `half` rotated pairs + (hd - rd) pass-through dims
+    // q heads: rotate in place
+    for (int i = threadIdx.x; i < nh * half; i += blockDim.x) {
+        const int h = i / half, j = i % half;
+        float s, c;
+        sincosf((float)pos * inv_freq[j], &s, &c);
+        T* p = qrow + h * hd;
+        const float x1 = to_float(p[j]), x2 = to_float(p[j + half]);
+        p[j] = from_float<T>(x1 * c - x2 * s);
+        p[j + half] = from_float<T>(x2 * c + x1 * s);
+    }
+    // k heads: rotate, keep in place (a layer that shares another layer's
+    // cache still sees its own rotated k in the activation buffer) and store
+    for (int i = threadIdx.x; i < nkv * pairs_per_head; i += blockDim.x) {
+        const int h = i / pairs_per_head, j = i % pairs_per_head;
+        T* p = krow + h * hd;
+        if (j < half) {
+            float s, c;
+            sincosf((float)pos * inv_freq[j], &s, &c);
+            const float x1 = to_float(p[j]), x2 = to_float(p[j + half]);
+            const T y1 = from_float<T>(x1 * c - x2 * s), y2 = from_float<T>(x2 * c + x1 * s);
+            p[j] = y1;
+            p[j + half] = y2;
+            if (store) {
+                kc[slot + h * hd + j] = y1;
+                kc[slot + h * hd + j + half] = y2;
+            }
+        } else if (store) {
+            const int d = j + half;          // dims rd .. hd-1 are not rotated
+            kc[slot + h * hd + d] = p[d];
+        }
+    }
+    if (store)
+        for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) vc[slot + i] = vrow[i];
+}
+
+}  // namespace prism
+
+// inv_freq may be null with rotary_dim 0: no rotation, only the cache store.
+// kc/vc may be null: only the rotation.
+PRISM_EXPORT int prism_rope_kv_write(void* q, void* k, const void* v, int dtype, int row_stride,
+                                     const int* positions, const int* tok_seg,
+                                     const float* inv_freq, int rotary_dim, void* kc, void* vc,
+                                     const int* block_table, int bt_width, int page_size,
+                                     int num_pages, int T, int nh, int nkv, int hd, int max_pos,
+                                     int* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+    const int threads = 128;
+    if (dtype == PRISM_DTYPE_BF16)
+        prism::rope_kv_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+            (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, positions,
+            tok_seg, inv_freq, rotary_dim, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table,
+            bt_width, page_size, num_pages, nh, nkv, hd, max_pos, err);
+    else
+        prism::rope_kv_kernel<float><<<T, threads, 0, stream>>>(
+            (float*)q, (float*)k, (const float*)v, row_stride, positions, tok_seg, inv_freq,
+            rotary_dim, (float*)kc, (float*)vc, block_table, bt_width, page_size, num_pages, nh,
+            nkv, hd, max_pos, err);
+    return (int)cudaPeekAtLastError();
+}

@@ -1,0 +1,31 @@
+// SwiGLU gate: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z * sigmoid(z),
+// gate columns first and up columns second (andre-fu/prism engine/executor.py:125-127;
+// fused buffer engine/weight_pool.py:194-197).  float32 arithmetic, one rounding at the store.
+#include "common.cuh"
+
+namespace prism {
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, i = idx % I;
+        const float g = to_float(gu[t * 2 * I + i]);
+        const float u = to_float(gu[t * 2 * I + I + i]);
+        out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+}  // namespace prism
+
+PRISM_EXPORT int prism_swiglu(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == PRISM_DTYPE_BF16)
+        prism::swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+    else
+        prism::swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    return (int)cudaPeekAtLastError();
+}

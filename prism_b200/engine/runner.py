@@ -1,0 +1,201 @@
+"""The step function: one batch of (request, its next tokens) in, logits at
+the wanted places out.
+
+It replaces andre-fu/prism's ``prefill`` / ``decode_step`` /
+``batched_decode_step`` (engine/executor.py:77,203,320): portions of prompts
+and single decode tokens are one flat batch, each token attends to its
+request's pages, and only the given tokens are computed.  A new token's key
+is stored at the slot equal to its position (the number of tokens cached
+before it); the reference's decode entry points advance the length first and
+so store one slot late (executor.py:205-208) - that is not reproduced.
+
+Pure-decode steps replay a CUDA graph captured per batch-size bucket
+(the reference: executor.py:164-201,272-310); rows added to fill a bucket use
+position 0 and the scratch page and their logits are dropped.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages, plan_groups
+from ..cache.storage import CacheStorage
+from ..models.decoder import DecoderModel
+from .batch import BatchLayout, Segment, StepContext, pack_batch
+
+
+class DeviceError(RuntimeError):
+    """A kernel met an index it must not follow (see csrc/common.cuh)."""
+
+
+_ERR_TEXT = {1: "token id outside the vocabulary", 2: "page id outside the pool",
+             3: "position outside max_position_embeddings", 4: "a kernel's bounded wait ran out"}
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, device, dtype: torch.dtype, page_size: int, num_pages: int,
+                 max_seqs: int, max_seq_len: Optional[int] = None, use_cuda_graph: bool = False,
+                 graph_batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)):
+        if not torch.cuda.is_available():
+            raise RuntimeError("prism_b200 needs a CUDA device; there is no CPU path")
+        self.model, self.device, self.dtype = model, torch.device(device), dtype
+        spec = model.spec
+        self.max_positions = spec.max_positions
+        self.max_seq_len = int(min(max_seq_len or spec.max_positions, spec.max_positions))
+        needs = model.cache_needs()
+        reads = [e.reads_cache_of for e in model.schedule]
+        self.groups, self.where = plan_groups(needs, reads)
+        self.paged_groups = [g.index for g in self.groups if g.kind == "paged"]
+        self.cache = CacheManager(self.groups, page_size, num_pages, max_seqs, self.max_seq_len)
+        self.storage = CacheStorage(self.groups, self.where, page_size, [num_pages] * len(self.groups),
+                                    max_seqs, self.device, dtype)
+        self.pad_page = {g: num_pages for g in self.paged_groups}     # the scratch page
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.use_cuda_graph = bool(use_cuda_graph)
+        self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]
+        self._graphs: Dict[int, dict] = {}
+        self.kernel_launch_estimate = 0
+
+    # ---- bookkeeping around a step -------------------------------------------
+    def begin_request(self, req_id) -> None:
+        self.cache.add_request(req_id)
+
+    def end_request(self, req_id) -> None:
+        self.cache.free_request(req_id)
+
+    def can_run(self, segments: Sequence[Segment]) -> bool:
+        reserve = [0] * len(self.groups)
+        for s in segments:
+            if not self.cache.can_append(s.req_id, len(s.tokens), reserve):
+                return False
+            for g, n in enumerate(self.cache.pages_needed(s.req_id, len(s.tokens))):
+                reserve[g] += n
+        return True
+
+    # ---- the step ----------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, segments: Sequence[Segment]) -> Optional[torch.Tensor]:
+        """Run the tokens of ``segments`` as one batch from the cache that
+        earlier steps left; append them to the cache; return float32 logits
+        ``[R, V]`` in the order of the segments and of their ``want`` lists
+        (None if nothing is wanted)."""
+        if not segments:
+            return None
+        for s in segments:
+            if len(s.tokens) < 1:
+                raise ValueError(f"request {s.req_id!r}: a segment needs at least one token")
+        if len({s.req_id for s in segments}) != len(segments):
+            raise ValueError("a request may appear once per step")
+        if not self.can_run(segments):
+            raise OutOfPages("Out of KV cache pages for this step")
+        for s in segments:
+            self.cache.append(s.req_id, len(s.tokens))
+        self.storage.clear_slots(self.cache.drain_fresh_slots())
+
+        tok, pos, seg_of, seg_start, cached, qlen, slots, rows = [], [], [], [0], [], [], [], []
+        for i, s in enumerate(segments):
+            c = self.cache.length(s.req_id)
+            n = len(s.tokens)
+            for w in s.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {s.req_id!r}: wanted place {w} outside its {n} tokens")
+                rows.append(len(tok) + w)
+            tok.extend(int(t) for t in s.tokens)
+            pos.extend(range(c, c + n))
+            seg_of.extend([i] * n)
+            seg_start.append(len(tok))
+            cached.append(c)
+            qlen.append(n)
+            slots.append(self.cache.slot(s.req_id))
+        block_rows = {g: [self.cache.block_table_row(s.req_id, g) for s in segments] for g in self.paged_groups}
+        max_q, max_kv = max(qlen), max(c + n for c, n in zip(cached, qlen))
+        host_meta = dict(seg_start=seg_start, cached_len=cached, q_len=qlen, slots=slots, tok_seg=seg_of)
+
+        S = len(segments)
+        if self.use_cuda_graph and max_q == 1 and S <= self.graph_batch_sizes[-1]:
+            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows)
+        else:
+            layout = BatchLayout(len(tok), S, len(rows), self.cache.table_width, self.paged_groups)
+            host = pack_batch(layout, tok, pos, seg_of, seg_start, cached, qlen, slots, rows,
+                              block_rows, self.pad_page)
+            dev = host.to(self.device, non_blocking=True)
+            ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions,
+                              host_meta, max_q, max_kv)
+            views = self.storage.views(ctx.block_tables, ctx.state_slots, slots)
+            logits = self.model.forward(ctx, views)
+        for s in segments:
+            self.cache.commit(s.req_id, len(s.tokens))
+        return logits
+
+    # ---- decode graphs ---------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in self.graph_batch_sizes:
+            if b >= n:
+                return b
+        raise ValueError(n)
+
+    def _capture(self, B: int) -> dict:
+        """Capture the decode step for a bucket of B one-token segments: static
+        descriptor buffer, every row's logits computed."""
+        layout = BatchLayout(B, B, B, self.cache.table_width, self.paged_groups)
+        dev = torch.zeros(layout.total, dtype=torch.int32, device=self.device)
+        pad_rows = {g: [[] for _ in range(B)] for g in self.paged_groups}
+        host = pack_batch(layout, [0] * B, [0] * B, list(range(B)), list(range(B + 1)), [0] * B, [1] * B,
+                          [self.cache.max_seqs] * B, list(range(B)), pad_rows, self.pad_page)
+        dev.copy_(host)
+        ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions, None,
+                          1, self.max_seq_len)
+        views = self.storage.views(ctx.block_tables, ctx.state_slots, None)
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):                       # warm-up: lazy library set-up happens outside capture
+                self.model.forward(ctx, views)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out = self.model.forward(ctx, views)
+        torch.cuda.synchronize(self.device)
+        return dict(graph=graph, layout=layout, dev=dev, out=out)
+
+    def _step_graph(self, tok, pos, cached, slots, rows, block_rows):
+        S = len(tok)
+        B = self._bucket(S)
+        g = self._graphs.get(B)
+        if g is None:
+            g = self._graphs[B] = self._capture(B)
+        pad = B - S
+        scratch_slot = self.cache.max_seqs
+        br = {k: v + [[] for _ in range(pad)] for k, v in block_rows.items()}
+        host = pack_batch(g["layout"], tok + [0] * pad, pos + [0] * pad, list(range(B)), list(range(B + 1)),
+                          cached + [0] * pad, [1] * B, slots + [scratch_slot] * pad, list(range(B)),
+                          br, self.pad_page)
+        g["dev"].copy_(host, non_blocking=True)
+        g["graph"].replay()
+        if not rows:
+            return None
+        out = g["out"]
+        if rows == list(range(S)):
+            return out[:S]
+        return out[torch.tensor(rows, device=self.device)]
+
+    def warmup_graphs(self, sizes: Optional[Sequence[int]] = None) -> None:
+        """Capture the decode graphs ahead of time (executor.py:312-318)."""
+        if self.use_cuda_graph:
+            for b in sizes or self.graph_batch_sizes:
+                if b not in self._graphs and b <= self.graph_batch_sizes[-1]:
+                    self._graphs[b] = self._capture(b)
+
+    def invalidate_graphs(self) -> None:
+        self._graphs.clear()
+
+    # ---- errors ---------------------------------------------------------------------
+    def check_errors(self) -> None:
+        """Read the device error word (synchronises) and raise if a kernel set it."""
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            raise DeviceError(f"device error {code}: {_ERR_TEXT.get(code, 'unknown')}")

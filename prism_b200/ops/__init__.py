@@ -1,0 +1,281 @@
+"""Python face of the hand-written CUDA kernels (``prism_b200/csrc``).
+
+Every function takes CUDA tensors, checks what the kernel assumes (dtype,
+contiguity, sizes), and launches on torch's current stream.  There is no CPU
+path and no library fallback: if the shared library cannot be built or
+loaded, or a tensor is not on a CUDA device, the call raises.
+
+Which of andre-fu/prism's call sites each op replaces:
+
+==================  ==========================================================
+``embed``           ``F.embedding`` (engine/executor.py:74-75)
+``add_rmsnorm``     residual add + ``fused_rms_norm`` (executor.py:108,122-124,130)
+``linear``          ``F.linear`` (executor.py:109,122,125,127,130)
+``rope_kv_write``   eager RoPE (executor.py:117-118) + the cache append inside
+                    ``flash_attn_with_kvcache`` (executor.py:119-120)
+``attention``       ``flash_attn_with_kvcache`` (executor.py:119-120)
+``swiglu``          ``F.silu(gate) * up`` (executor.py:127)
+``sample``          argmax / softmax + multinomial (engine/scheduler.py:266-272)
+==================  ==========================================================
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import threading
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+_lib = None
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or a launch failed."""
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def lib():
+    """The loaded shared library; built at the first call if it is missing or stale."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = _build.build(verbose=True)
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the prism_b200 CUDA kernels from {path}: {e}") from e
+        for name in dir(_Sig):
+            if name.startswith("prism_"):
+                fn = getattr(_lib, name)
+                fn.restype = ctypes.c_int
+                fn.argtypes = getattr(_Sig, name)
+    return _lib
+
+
+def library_file() -> Optional[str]:
+    return _build.library_path()
+
+
+_p, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+class _Sig:
+    prism_embed = [_p, _p, _i, _p, _i, _i, _i, _p, _p]
+    prism_add_rmsnorm = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _p, _i, _i, _p]
+    prism_rope_kv_write = [_p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i,
+                           _i, _i, _p, _p]
+    prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
+                               _i, _f, _p, _p]
+    prism_swiglu = [_p, _p, _i, _i, _i, _p]
+    prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
+    prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("prism_b200 kernels run on CUDA tensors only; there is no CPU path")
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        if code == 1:       # cudaErrorInvalidValue: the launcher refused the sizes
+            raise KernelError(f"{what}: sizes not supported by this kernel")
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+# --------------------------------------------------------------------------
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
+    """``out[t] = table[ids[t]]`` as float32.  ids int32 [T]; table [V, H]."""
+    _cuda(ids, table, out)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32
+    assert table.is_contiguous() and out.is_contiguous()
+    T, (V, H) = ids.shape[0], table.shape
+    assert out.shape == (T, H)
+    _check(lib().prism_embed(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, _ptr(err),
+                             _stream()), "embed")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None):
+    """``residual += delta`` in place (float32; ``delta`` None, ``[T, H]`` or a
+    stack ``[k, T, H]`` of partial sums), then ``out = rmsnorm(residual) * weight``
+    for every row, or for the rows listed in ``rows`` (int32)."""
+    _cuda(residual, delta, weight, out, rows)
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
+    T, H = residual.shape
+    nsplit, stride = 0, 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == (T, H)
+        nsplit = 1 if delta.dim() == 2 else delta.shape[0]
+        stride = T * H
+    n = T if rows is None else rows.shape[0]
+    assert out.shape == (n, H) and weight.shape == (H,)
+    _check(lib().prism_add_rmsnorm(_ptr(residual), _ptr(delta), F32 if delta is None else _dt(delta),
+                                   nsplit, stride, _ptr(weight), _dt(weight), float(eps), _ptr(out),
+                                   _dt(out), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+
+
+def sgemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor):
+    """True float32 ``out = x @ w.T + bias`` on CUDA cores."""
+    _cuda(x, w, bias, out)
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32
+    assert x.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    _check(lib().prism_sgemm_nt(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias),
+                                F32 if bias is None else _dt(bias), _ptr(out), out.stride(0), M, N, K,
+                                _stream()), "sgemm")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ w.T + bias`` with ``w`` in the ``[out, in]`` layout of the model
+    file.  float32 activations, or a float32 weight under bf16 activations
+    (a tensor the model file stores in 32-bit), go through the true-float32
+    kernel; bf16 x bf16 goes to the library matrix product (cuBLAS through
+    torch), as in andre-fu/prism (executor.py:109)."""
+    _cuda(x, w, bias)
+    M, N = x.shape[0], w.shape[0]
+    want = out_dtype or (out.dtype if out is not None else x.dtype)
+    if x.dtype == torch.float32 or w.dtype == torch.float32:
+        x32 = x if x.dtype == torch.float32 else x.float()
+        w32 = w if w.dtype == torch.float32 else w.float()
+        o32 = out if (out is not None and out.dtype == torch.float32) else \
+            torch.empty((M, N), dtype=torch.float32, device=x.device)
+        sgemm(x32, w32, bias, o32)
+        if want == torch.float32:
+            return o32
+        if out is not None:
+            out.copy_(o32)
+            return out
+        return o32.to(want)
+    # bf16 x bf16, library product with float32 accumulation
+    if want == torch.float32:
+        res = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if bias is not None:
+            res += bias.float()
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    b = bias if (bias is None or bias.dtype == torch.bfloat16) else bias.to(torch.bfloat16)
+    if out is None:
+        return torch.nn.functional.linear(x, w, b)
+    if b is None:
+        return torch.mm(x, w.t(), out=out)
+    return torch.addmm(b, x, w.t(), out=out)
+
+
+def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor,
+                  tok_seg: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                  k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                  block_table: Optional[torch.Tensor], num_pages: int, max_pos: int,
+                  err: torch.Tensor):
+    """Rotate ``q [T, nh, hd]`` and ``k [T, nkv, hd]`` in place (views of one
+    row-strided buffer) and store k, v at their positions in the paged cache
+    ``[pages, P, nkv, hd]``.  ``k_cache`` None: rotate only."""
+    _cuda(q, k, v, positions, tok_seg, inv_freq, k_cache, v_cache, block_table)
+    T, nh, hd = q.shape
+    nkv = k.shape[1]
+    rs = q.stride(0)
+    assert k.stride(0) == rs and v.stride(0) == rs, "q, k, v must be views of one buffer"
+    assert q.stride(2) == 1 and q.stride(1) == hd and k.stride(1) == hd and v.stride(1) == hd
+    assert positions.dtype == torch.int32 and tok_seg.dtype == torch.int32
+    P = W = 0
+    if k_cache is not None:
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == q.dtype
+        assert k_cache.shape[2:] == (nkv, hd) and block_table.dtype == torch.int32
+        P, W = k_cache.shape[1], block_table.shape[1]
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float32 and inv_freq.shape[0] * 2 == rotary_dim
+    _check(lib().prism_rope_kv_write(_ptr(q), _ptr(k), _ptr(v), _dt(q), rs, _ptr(positions),
+                                     _ptr(tok_seg), _ptr(inv_freq), rotary_dim, _ptr(k_cache),
+                                     _ptr(v_cache), _ptr(block_table), W, P, num_pages, T, nh, nkv,
+                                     hd, max_pos, _ptr(err), _stream()), "rope_kv_write")
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
+                      tok_seg: torch.Tensor, num_pages: int, window: Optional[int], scale: float,
+                      err: torch.Tensor):
+    """Shape-generic paged causal GQA attention; ``q [T, nh, hd]`` row-strided,
+    ``out [T, nh*hd]``."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, tok_seg)
+    T, nh, hd = q.shape
+    nkv, P = k_cache.shape[2], k_cache.shape[1]
+    assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1
+    assert k_cache.dtype == q.dtype and out.dtype == q.dtype
+    if hd > 256:
+        raise KernelError(f"attention: head_dim {hd} > 256 is not supported")
+    _check(lib().prism_attention_generic(_ptr(q), q.stride(0), _ptr(out), out.stride(0),
+                                         _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(block_table),
+                                         block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, nh,
+                                         nkv, hd, P, num_pages, int(window or 0), float(scale),
+                                         _ptr(err), _stream()), "attention_generic")
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor):
+    """``out = silu(gu[:, :I]) * gu[:, I:]``."""
+    _cuda(gu, out)
+    T, I2 = gu.shape
+    assert gu.is_contiguous() and out.is_contiguous() and out.shape == (T, I2 // 2) and out.dtype == gu.dtype
+    _check(lib().prism_swiglu(_ptr(gu), _ptr(out), _dt(gu), T, I2 // 2, _stream()), "swiglu")
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optional[torch.Tensor],
+           out: torch.Tensor):
+    """Per row: argmax if its temperature <= 0, else inverse-CDF sampling of
+    ``softmax(logits / temperature)`` at the uniform number ``u``."""
+    _cuda(logits, temperature, u, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    R, V = logits.shape
+    _check(lib().prism_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(u),
+                              _ptr(out), _stream()), "sample")
+
+
+# --------------------------------------------------------------------------
+# composites: the places where a faster kernel is chosen for a shape
+# --------------------------------------------------------------------------
+
+def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[int], scale: float):
+    """Attention of the step's tokens over one cache plane.  ``cache`` is a
+    ``PagedCacheView``; the kernel is chosen by dtype and shape, and the
+    shape-generic kernel takes whatever the faster ones refuse."""
+    attention_generic(q, out, cache.k, cache.v, cache.block_table, ctx.positions, ctx.tok_seg,
+                      cache.num_pages, window, scale, ctx.err)
+
+
+def feed_forward_swiglu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor):
+    """``down(silu(gate(x)) * up(x))`` with the fused gate/up weight."""
+    gu = linear(x, gate_up_w)
+    act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
+    swiglu(gu, act)
+    return linear(act, down_w)

@@ -1,0 +1,48 @@
+"""The engine against the plain implementation for every way of cutting the
+work, in float32 and in bfloat16 (GPU)."""
+
+import pytest
+import torch
+
+from helpers import (TINY, compare_with_plain, model_folder, random_tokens, run_trace, trace_budget,
+                     trace_mixed, trace_portions, trace_tail, trace_whole)
+
+pytestmark = pytest.mark.gpu
+
+# float32: the engine and the plain model differ by the order of float32 additions only.
+# bfloat16: activations are rounded to 8 bits of mantissa where they are stored
+# (norm out, qkv, attention out, SwiGLU out); weights are the same bf16 values on both sides.
+TOL = {"float32": dict(atol=2e-5, rtol=1e-5), "bfloat16": dict(atol=2e-3, rtol=3e-2)}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71, 130], "C": [3, 30, 64, 97, 150]}
+
+
+def make_runner(name, dtype, num_pages, page_size=None, max_seqs=8):
+    from prism_b200.weights.loader import load_model_folder
+    from prism_b200.engine.runner import ModelRunner
+    tdt = getattr(torch, dtype)
+    cfg, model, pool = load_model_folder(model_folder(name), "cuda:0", tdt)
+    ps = page_size or TINY[name][2]
+    runner = ModelRunner(model, "cuda:0", tdt, ps, num_pages, max_seqs, use_cuda_graph=False)
+    runner._pool = pool
+    return runner
+
+
+def sequences(name):
+    vocab = TINY[name][0]["vocab_size"]
+    return {f"r{i}": random_tokens(vocab, n, 100 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cutting(name, dtype, mode):
+    seqs = sequences(name)
+    steps = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions,
+             "mixed": lambda s: trace_mixed(s, seed=7)}[mode](seqs)
+    ps = TINY[name][2]
+    budget = trace_budget(steps, ps)
+    runner = make_runner(name, dtype, num_pages=budget // ps)
+    got = run_trace(runner, steps)
+    assert len(got) == sum(len(s) for s in seqs.values())
+    compare_with_plain(name, seqs, got, **TOL[dtype])
+    assert runner.cache.pages_in_use() == 0
