@@ -206,7 +206,7 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: 
     T, nh, hd = q.shape
     nkv = k.shape[1]
     rs = q.stride(0)
-    assert k.stride(0) == rs and v.stride(0) == rs, "q, k, v must be views of one buffer"
+    assert T == 1 or (k.stride(0) == rs and v.stride(0) == rs), "q, k, v must be views of one buffer"
     assert q.stride(2) == 1 and q.stride(1) == hd and k.stride(1) == hd and v.stride(1) == hd
     assert positions.dtype == torch.int32 and tok_seg.dtype == torch.int32
     P = W = 0
