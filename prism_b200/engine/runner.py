@@ -56,7 +56,7 @@ class ModelRunner:
         self.use_cuda_graph = bool(use_cuda_graph)
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]
         self._graphs: Dict[int, dict] = {}
-        self.kernel_launch_estimate = 0
+        self.graph_kernel_launches = 0       # kernels of this library replayed inside graphs
 
     # ---- bookkeeping around a step -------------------------------------------
     def begin_request(self, req_id) -> None:
@@ -156,10 +156,12 @@ class ModelRunner:
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        from .. import ops
+        before = ops.launch_count
         with torch.cuda.graph(graph, stream=stream):
             out = self.model.forward(ctx, views)
         torch.cuda.synchronize(self.device)
-        return dict(graph=graph, layout=layout, dev=dev, out=out)
+        return dict(graph=graph, layout=layout, dev=dev, out=out, launches=ops.launch_count - before)
 
     def _step_graph(self, tok, pos, cached, slots, rows, block_rows):
         S = len(tok)
@@ -175,6 +177,7 @@ class ModelRunner:
                           br, self.pad_page)
         g["dev"].copy_(host, non_blocking=True)
         g["graph"].replay()
+        self.graph_kernel_launches += g["launches"]
         if not rows:
             return None
         out = g["out"]

@@ -102,7 +102,12 @@ def _cuda(*ts):
             raise KernelError("prism_b200 kernels run on CUDA tensors only; there is no CPU path")
 
 
+launch_count = 0      # kernels of this library launched (or captured) by this process
+
+
 def _check(code: int, what: str):
+    global launch_count
+    launch_count += 1
     if code != 0:
         if code == 1:       # cudaErrorInvalidValue: the launcher refused the sizes
             raise KernelError(f"{what}: sizes not supported by this kernel")
