@@ -1,0 +1,78 @@
+// Warp-level tensor-core and async-copy helpers shared by the bf16 attention
+// kernels: m16n8k16 bf16 MMA with float32 accumulation, ldmatrix fragment
+// loads, 16-byte cp.async, and a loader that gathers a tile of cache rows
+// through a request's block table into padded shared memory.
+#pragma once
+
+#include "common.cuh"
+
+namespace prism {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;      // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem)));
+}
+
+// d += a (16x16, row) * b (16x8, col), bf16 in, float32 accumulate
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Rows of a shared-memory tile are padded by 8 bf16 (16 bytes): with a row of
+// HD bf16 (HD a multiple of 16) eight consecutive rows then start in eight
+// different 16-byte bank groups, which is what ldmatrix needs.
+template <int HD> struct TileRow { static constexpr int STRIDE = HD + 8; };
+
+// Gather `rows` cache rows (keys first_key .. first_key + rows - 1 of one
+// kv head) into smem[rows][HD + 8].  Keys outside [lo, hi] are zero-filled.
+// A page id outside the pool is reported and the row zero-filled.
+template <int HD, int ROWS, int THREADS>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* smem, const __nv_bfloat16* __restrict__ cache,
+                                             const int* __restrict__ bt, int first_key, int lo, int hi,
+                                             int page_size, int num_pages, int nkv, int kvh, int* err) {
+    constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
+    constexpr int TOTAL = ROWS * CHUNKS;
+    for (int i = threadIdx.x; i < TOTAL; i += THREADS) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        const int key = first_key + r;
+        bool valid = key >= lo && key <= hi;
+        const __nv_bfloat16* src = cache;
+        if (valid) {
+            const int page = bt[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                report_error(err, PRISM_ERR_PAGE_RANGE);
+                valid = false;
+            } else {
+                src = cache + (((size_t)page * page_size + key % page_size) * nkv + kvh) * HD + c * 8;
+            }
+        }
+        cp_async16(smem + r * TileRow<HD>::STRIDE + c * 8, src, valid);
+    }
+}
+
+}  // namespace prism

@@ -83,6 +83,11 @@ class _Sig:
                            _i, _i, _p, _p]
     prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                _i, _f, _p, _p]
+    prism_attention_bf16_supported = [_i, _i, _i]
+    prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
+                                   _p, _p, _i, _p, _p]
+    prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
+                                    _f, _p, _p]
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
@@ -270,10 +275,77 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optiona
 # composites: the places where a faster kernel is chosen for a shape
 # --------------------------------------------------------------------------
 
+NUM_SMS = 148
+FORCE_GENERIC_ATTENTION = os.environ.get("PRISM_ATTENTION", "") == "generic"
+
+
+def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
+                          scale, nsplit, part_o, part_ml, err):
+    """Tensor-core decode attention (one token per request) with the keys split
+    over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
+    ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, tok_seg, part_o, part_ml)
+    T, nh, hd = q.shape
+    nkv, P = k_cache.shape[2], k_cache.shape[1]
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1
+    assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
+    assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
+    _check(lib().prism_attention_decode_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache),
+                                             _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+                                             _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
+                                             int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
+                                             int(nsplit), _ptr(err), _stream()), "attention_decode_bf16")
+    global launch_count
+    launch_count += 1          # the merge kernel
+
+
+def attention_prefill_bf16(q, out, k_cache, v_cache, block_table, seg_start, cached_len, max_q_len,
+                           num_pages, window, scale, err):
+    """Tensor-core attention for segments of any length (portions of prompts,
+    and single tokens among them)."""
+    _cuda(q, out, k_cache, v_cache, block_table, seg_start, cached_len)
+    T, nh, hd = q.shape
+    nkv, P = k_cache.shape[2], k_cache.shape[1]
+    S = cached_len.shape[0]
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1 and seg_start.shape[0] == S + 1
+    _check(lib().prism_attention_prefill_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache),
+                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+                                              _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, hd,
+                                              P, num_pages, int(window or 0), float(scale), _ptr(err),
+                                              _stream()), "attention_prefill_bf16")
+
+
+def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
+    return bool(lib().prism_attention_bf16_supported(hd, nh, nkv))
+
+
+def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> int:
+    """How many CTAs share one (token, kv head)'s keys: enough to put two CTAs
+    on every SM, at most one per 64-key tile."""
+    span = min(max_kv_len, window + 64) if window else max_kv_len
+    tiles = max(1, (span + 63) // 64)
+    return max(1, min(tiles, 64, -(-2 * NUM_SMS // max(1, T * nkv))))
+
+
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[int], scale: float):
     """Attention of the step's tokens over one cache plane.  ``cache`` is a
     ``PagedCacheView``; the kernel is chosen by dtype and shape, and the
     shape-generic kernel takes whatever the faster ones refuse."""
+    T, nh, hd = q.shape
+    nkv = cache.k.shape[2]
+    if q.dtype == torch.bfloat16 and not FORCE_GENERIC_ATTENTION and attention_bf16_supported(hd, nh, nkv):
+        if ctx.decode_only:
+            nsplit = decode_splits(T, nkv, ctx.max_kv_len, window)
+            part_o = ctx.alloc((T, nh, nsplit, hd), torch.float32)
+            part_ml = ctx.alloc((T, nh, nsplit, 2), torch.float32)
+            attention_decode_bf16(q, out, cache.k, cache.v, cache.block_table, ctx.positions, ctx.tok_seg,
+                                  cache.num_pages, window, scale, nsplit, part_o, part_ml, ctx.err)
+        else:
+            attention_prefill_bf16(q, out, cache.k, cache.v, cache.block_table, ctx.seg_start, ctx.cached_len,
+                                   ctx.max_q_len, cache.num_pages, window, scale, ctx.err)
+        return
     attention_generic(q, out, cache.k, cache.v, cache.block_table, ctx.positions, ctx.tok_seg,
                       cache.num_pages, window, scale, ctx.err)
 

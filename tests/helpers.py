@@ -34,7 +34,12 @@ TINY_C = dict(architectures=ARCH, model_type="qwen2", num_hidden_layers=4, hidde
               vocab_size=389, rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False,
               max_position_embeddings=512, use_sliding_window=True, sliding_window=24,
               max_window_layers=2, attention_bias=False)
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16)}    # config, weight seed, page size
+# D: head size 64, which the tensor-core attention kernels take in bfloat16; window on every layer but the first
+TINY_D = dict(architectures=ARCH, model_type="qwen2", num_hidden_layers=2, hidden_size=136,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=200,
+              vocab_size=301, rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=True,
+              max_position_embeddings=1024, use_sliding_window=True, sliding_window=70, max_window_layers=1)
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 32)}    # config, weight seed, page size
 
 _folders = {}
 

@@ -1,0 +1,386 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 reference of the same
+op, at sizes other than the tiny engine configurations use (GPU)."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from prism_b200 import ops
+    return ops
+
+
+def _err():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# --------------------------------------------------------------------------
+# references
+# --------------------------------------------------------------------------
+
+def ref_rmsnorm(x, w, eps):
+    x = x.float()
+    return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+
+
+def ref_rope(x, positions, inv_freq, rd):
+    """x [T, heads, hd] float32; rotate-half pairing over the first rd dims."""
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2 = x[..., :rd // 2], x[..., rd // 2:rd]
+    out = x.clone()
+    out[..., :rd // 2] = x1 * cos - x2 * sin
+    out[..., rd // 2:rd] = x2 * cos + x1 * sin
+    return out
+
+
+def ref_paged_attention(q, k_cache, v_cache, block_table, positions, tok_seg, window, scale):
+    """q [T, nh, hd]; caches [pages, P, nkv, hd]; float32 math, one token at a time."""
+    T, nh, hd = q.shape
+    P, nkv = k_cache.shape[1], k_cache.shape[2]
+    g = nh // nkv
+    kf = k_cache.float().reshape(-1, nkv, hd)
+    vf = v_cache.float().reshape(-1, nkv, hd)
+    out = torch.empty(T, nh, hd, dtype=torch.float32, device=q.device)
+    for t in range(T):
+        pos, seg = int(positions[t]), int(tok_seg[t])
+        lo = max(0, pos - window + 1) if window else 0
+        idx = torch.arange(lo, pos + 1, device=q.device)
+        rows = block_table[seg][idx // P].long() * P + idx % P
+        K = kf[rows].repeat_interleave(g, dim=1)          # [n, nh, hd]
+        V = vf[rows].repeat_interleave(g, dim=1)
+        s = torch.einsum("hd,nhd->hn", q[t].float(), K) * scale
+        p = torch.softmax(s, dim=-1)
+        out[t] = torch.einsum("hn,nhd->hd", p, V)
+    return out.reshape(T, nh * hd)
+
+
+class PagedCase:
+    """Random requests laid out in a paged cache whose unused slots hold NaN,
+    so that a read of a slot that no request owns (a wrong page, an unmasked
+    tail of a page) poisons the output."""
+
+    def __init__(self, segs, nh, nkv, hd, P, dtype, seed, num_pages=None, table_width=None):
+        # segs: list of (cached_len, q_len)
+        g = torch.Generator().manual_seed(seed)
+        self.S = len(segs)
+        total_pages = sum((c + n + P - 1) // P for c, n in segs)
+        self.num_pages = num_pages or total_pages + 3
+        W = table_width or max((c + n + P - 1) // P for c, n in segs) + 2
+        perm = torch.randperm(self.num_pages, generator=g).tolist()
+        self.k = torch.full((self.num_pages, P, nkv, hd), float("nan"), dtype=dtype, device=DEV)
+        self.v = torch.full((self.num_pages, P, nkv, hd), float("nan"), dtype=dtype, device=DEV)
+        bt = torch.full((self.S, W), -7, dtype=torch.int32)
+        pos, seg_of, seg_start, cached, qlens = [], [], [0], [], []
+        for s, (c, n) in enumerate(segs):
+            for i in range((c + n + P - 1) // P):
+                bt[s, i] = perm.pop()
+            L = c + n
+            kk = (torch.randn(L, nkv, hd, generator=g)).to(dtype)
+            vv = (torch.randn(L, nkv, hd, generator=g)).to(dtype)
+            idx = torch.arange(L)
+            rows = (bt[s][idx // P].long() * P + idx % P).to(DEV)
+            self.k.view(-1, nkv, hd)[rows] = kk.to(DEV)
+            self.v.view(-1, nkv, hd)[rows] = vv.to(DEV)
+            pos += list(range(c, c + n))
+            seg_of += [s] * n
+            seg_start.append(seg_start[-1] + n)
+            cached.append(c)
+            qlens.append(n)
+        self.T = len(pos)
+        self.q = (torch.randn(self.T, nh, hd, generator=g)).to(dtype).to(DEV)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        self.bt = bt.to(DEV)
+        self.positions, self.tok_seg = i32(pos), i32(seg_of)
+        self.seg_start, self.cached_len = i32(seg_start), i32(cached)
+        self.max_q = max(qlens)
+        self.max_kv = max(c + n for c, n in segs)
+
+
+# --------------------------------------------------------------------------
+# elementwise / norm / rope / embed / gemm / sample
+# --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("T,H,V", [(5, 200, 77), (33, 3584, 1000)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(T, H, V, dtype):
+    ops = _ops()
+    table = _rand((V, H), dtype, 1)
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2)).to(torch.int32).to(DEV)
+    out = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    err = _err()
+    ops.embed(ids, table, out, err)
+    assert torch.equal(out, table[ids.long()].float()) and int(err) == 0
+    ids[1] = V                                        # outside the vocabulary: flagged, row zeroed, no fault
+    ops.embed(ids, table, out, err)
+    assert int(err) == 1 and float(out[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("T,H", [(3, 96), (17, 1000), (64, 3584), (2, 8192)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nsplit", [0, 1, 3])
+def test_add_rmsnorm(T, H, dtype, nsplit):
+    ops = _ops()
+    eps = 3e-6
+    res = _rand((T, H), torch.float32, 3)
+    w = _rand((H,), dtype, 4) + 1
+    ref_res = res.clone()
+    delta = None
+    if nsplit == 1:
+        delta = _rand((T, H), dtype, 5)
+        ref_res = ref_res + delta.float()
+    elif nsplit > 1:
+        delta = _rand((nsplit, T, H), torch.float32, 5)
+        ref_res = ref_res + delta.sum(0)
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(res, delta, w, eps, out)
+    ref = ref_rmsnorm(ref_res, w, eps)
+    assert torch.allclose(res, ref_res, atol=1e-6, rtol=1e-6)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(out.float(), ref, atol=tol, rtol=tol)
+    # rows: only the listed rows are normed
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(res, None, w, eps, out2, rows)
+    assert torch.allclose(out2.float(), ref[[T - 1, 0]], atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 100, 96), (7, 333, 224), (16, 64, 64), (65, 129, 100), (200, 520, 3584)])
+def test_sgemm(M, N, K):
+    ops = _ops()
+    x, w, b = _rand((M, K), torch.float32, 6), _rand((N, K), torch.float32, 7, 0.05), _rand((N,), torch.float32, 8)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.sgemm(x, w, b, out)
+    ref = (x.double() @ w.double().T + b.double()).float()
+    assert torch.allclose(out, ref, atol=2e-5, rtol=1e-5)
+    # a row's result does not depend on the batch it is in
+    out1 = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    ops.sgemm(x[M // 2:M // 2 + 1].contiguous(), w, b, out1)
+    assert torch.equal(out1[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 152, 96), (8, 4608, 3584), (300, 1000, 512)])
+def test_linear_bf16(M, N, K):
+    ops = _ops()
+    x, w, b = _rand((M, K), torch.bfloat16, 6), _rand((N, K), torch.bfloat16, 7, 0.05), _rand((N,), torch.bfloat16, 8)
+    ref = x.float() @ w.float().T + b.float()
+    out = ops.linear(x, w, b)
+    assert out.dtype == torch.bfloat16 and torch.allclose(out.float(), ref, atol=3e-2, rtol=2e-2)
+    out32 = ops.linear(x, w, None, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and torch.allclose(out32, x.float() @ w.float().T, atol=2e-3, rtol=2e-3)
+    # a weight the file stores in 32-bit stays so and goes through the float32 kernel
+    out_mixed = ops.linear(x, w.float(), b)
+    assert out_mixed.dtype == torch.bfloat16 and torch.allclose(out_mixed.float(), ref, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("T,I", [(3, 100), (40, 18944)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(T, I, dtype):
+    ops = _ops()
+    gu = _rand((T, 2 * I), dtype, 9, 2.0)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :I].float(), gu[:, I:].float()
+    ref = g * torch.sigmoid(g) * u
+    tol = 1e-6 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(out.float(), ref, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rd,P", [(5, 1, 48, 48, 8), (28, 4, 128, 128, 256), (6, 3, 80, 32, 16), (2, 2, 16, 0, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_kv_write(nh, nkv, hd, rd, P, dtype):
+    ops = _ops()
+    T, S, W = 23, 3, 40
+    pages = S * W
+    qkv = _rand((T, (nh + 2 * nkv) * hd), dtype, 10)
+    before = qkv.clone()
+    q = qkv[:, :nh * hd].view(T, nh, hd)
+    k = qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    g = torch.Generator().manual_seed(11)
+    tok_seg = torch.sort(torch.randint(0, S, (T,), generator=g)).values.to(torch.int32)
+    positions = torch.zeros(T, dtype=torch.int32)
+    start = [0, 100, 7]
+    for s in range(S):
+        n = int((tok_seg == s).sum())
+        positions[tok_seg == s] = torch.arange(start[s], start[s] + n, dtype=torch.int32)
+    # the positions used below touch distinct pages per request
+    bt = torch.arange(S * W, dtype=torch.int32).view(S, W) % pages
+    kc = torch.zeros(pages, P, nkv, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    theta = 1e6
+    inv = (1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))).to(DEV) if rd else None
+    err = _err()
+    ops.rope_kv_write(q, k, v, positions.to(DEV), tok_seg.to(DEV), inv, rd, kc, vc, bt.to(DEV), pages, 10 ** 6, err)
+    assert int(err) == 0
+    bq = before[:, :nh * hd].view(T, nh, hd).float()
+    bk = before[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd).float()
+    bv = before[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    rq = ref_rope(bq, positions.to(DEV), inv, rd) if rd else bq
+    rk = ref_rope(bk, positions.to(DEV), inv, rd) if rd else bk
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(q.float(), rq, atol=tol, rtol=tol)
+    assert torch.allclose(k.float(), rk, atol=tol, rtol=tol)
+    for t in range(T):
+        s, p = int(tok_seg[t]), int(positions[t])
+        page = int(bt[s, p // P])
+        assert torch.equal(kc[page, p % P], k[t]) and torch.equal(vc[page, p % P], bv[t])
+    assert int((kc != 0).any(dim=-1).any(dim=-1).sum()) <= T      # nothing else was written
+
+
+def test_sample_greedy_and_temperature():
+    ops = _ops()
+    R, V = 9, 152064 // 8 + 5
+    logits = _rand((R, V), torch.float32, 12, 3.0)
+    logits[3, 100] = logits[3, 7] = logits[3].max() + 1           # a tie: the lowest index wins
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, None, None, out)
+    ref = logits.argmax(-1)
+    ref[3] = 7
+    assert torch.equal(out.long(), ref)
+    temps = torch.tensor([0.7, 0.0, 1.3, 0.2, 1.0, 0.5, 2.0, 0.9, 1.1], device=DEV)
+    us = torch.tensor([0.0, 0.5, 0.999999, 0.3, 0.25, 0.75, 0.5, 0.1, 0.9], device=DEV)
+    ops.sample(logits, temps, us, out)
+    for r in range(R):
+        if temps[r] <= 0:
+            assert int(out[r]) == int(ref[r])
+            continue
+        p = torch.softmax(logits[r].double() / float(temps[r]), -1)
+        c = torch.cumsum(p, -1)
+        tok = int(out[r])
+        lo = float(c[tok - 1]) if tok > 0 else 0.0
+        # the drawn token's cumulative interval contains u (to float32 rounding of the sums)
+        assert lo - 1e-4 <= float(us[r]) <= float(c[tok]) + 1e-4, (r, tok, lo, float(us[r]), float(c[tok]))
+
+
+# --------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------
+
+GENERIC_CASES = [
+    # nh, nkv, hd, P, window, segs (cached, q_len)
+    (5, 1, 48, 8, None, [(0, 19), (37, 1), (5, 6)]),
+    (6, 3, 80, 16, 11, [(0, 40), (30, 1), (16, 16)]),
+    (28, 4, 128, 64, None, [(100, 3), (0, 70)]),
+    (3, 3, 16, 4, 5, [(0, 9), (9, 2)]),
+    (2, 1, 256, 32, None, [(50, 2)]),
+]
+
+
+@pytest.mark.parametrize("case", GENERIC_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(case, dtype):
+    ops = _ops()
+    nh, nkv, hd, P, window, segs = case
+    c = PagedCase(segs, nh, nkv, hd, P, dtype, seed=20)
+    out = torch.empty(c.T, nh * hd, dtype=dtype, device=DEV)
+    err = _err()
+    scale = hd ** -0.5
+    ops.attention_generic(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, err)
+    ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
+    assert int(err) == 0 and not torch.isnan(out.float()).any()
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(out.float(), ref, atol=tol, rtol=tol)
+
+
+def test_attention_generic_rejects_big_head():
+    ops = _ops()
+    c = PagedCase([(0, 2)], 1, 1, 272, 16, torch.float32, seed=1)
+    with pytest.raises(ops.KernelError):
+        ops.attention_generic(c.q, torch.empty(2, 272, device=DEV), c.k, c.v, c.bt, c.positions, c.tok_seg,
+                              c.num_pages, None, 1.0, _err())
+
+
+DECODE_CASES = [
+    # nh, nkv, hd, P, window, contexts (cached lens; one new token each), nsplit
+    (28, 4, 128, 256, None, [2048, 1, 0, 255, 256, 257, 4000], 10),
+    (28, 4, 128, 64, None, [63, 64, 65, 1000], 1),
+    (8, 8, 64, 16, None, [5, 300, 129], 3),
+    (16, 1, 64, 32, 100, [99, 100, 101, 700, 3], 7),
+    (14, 2, 128, 8, 64, [1500, 64, 63], 64),
+    (40, 8, 128, 256, None, [3000], 33),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_attention_decode_bf16(case):
+    ops = _ops()
+    nh, nkv, hd, P, window, ctxs, nsplit = case
+    c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=21)
+    out = torch.empty(c.T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    part_o = torch.full((c.T, nh, nsplit, hd), float("nan"), device=DEV)
+    part_ml = torch.full((c.T, nh, nsplit, 2), float("nan"), device=DEV)
+    err = _err()
+    scale = hd ** -0.5
+    ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
+                              nsplit, part_o, part_ml, err)
+    ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
+    assert int(err) == 0 and not torch.isnan(out.float()).any()
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+
+
+PREFILL_CASES = [
+    (28, 4, 128, 256, None, [(0, 200), (300, 1), (64, 64), (5, 63), (0, 1), (1000, 65)]),
+    (8, 8, 64, 16, None, [(0, 130), (17, 2)]),
+    (16, 1, 64, 32, 50, [(0, 180), (49, 3), (50, 1), (400, 70)]),
+    (14, 2, 128, 8, 64, [(100, 129), (0, 64)]),
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES)
+def test_attention_prefill_bf16(case):
+    ops = _ops()
+    nh, nkv, hd, P, window, segs = case
+    c = PagedCase(segs, nh, nkv, hd, P, torch.bfloat16, seed=22)
+    out = torch.full((c.T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = _err()
+    scale = hd ** -0.5
+    ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                               window, scale, err)
+    ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
+    assert int(err) == 0 and not torch.isnan(out.float()).any()
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+
+
+@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill"])
+def test_attention_finds_one_far_key(kind):
+    """One key among thousands carries the whole softmax: the query and that
+    key are scaled so that its score stands out, and its value is marked.  A
+    kernel that drops a tile, a split or a page loses the mark."""
+    ops = _ops()
+    nh, nkv, hd, P = 8, 2, 64, 16
+    dtype = torch.float32 if kind == "generic32" else torch.bfloat16
+    ctx = 3000
+    segs = [(ctx, 1)] if kind != "prefill" else [(ctx - 40, 41)]
+    for far in (0, 17, 1234, 2047, 2048, ctx - 1, ctx):
+        c = PagedCase(segs, nh, nkv, hd, P, dtype, seed=23)
+        c.q[:] = 0
+        c.q[-1, :, 0] = 30.0                      # the last query looks along dim 0
+        page, off = int(c.bt[0, far // P]), far % P
+        c.k[page, off, :, 0] = 30.0               # the far key answers: score 900 * scale
+        c.v[page, off] = 5.0
+        out = torch.empty(c.T, nh * hd, dtype=dtype, device=DEV)
+        err = _err()
+        scale = hd ** -0.5
+        if kind.startswith("generic"):
+            ops.attention_generic(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, None, scale, err)
+        elif kind == "decode":
+            ns = 9
+            ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, None, scale, ns,
+                                      torch.empty(c.T, nh, ns, hd, device=DEV), torch.empty(c.T, nh, ns, 2, device=DEV), err)
+        else:
+            ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                                       None, scale, err)
+        assert int(err) == 0
+        assert torch.allclose(out[-1].float(), torch.full_like(out[-1].float(), 5.0), atol=0.05), (kind, far, out[-1][:4])

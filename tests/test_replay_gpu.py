@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 # bfloat16: activations are rounded to 8 bits of mantissa where they are stored
 # (norm out, qkv, attention out, SwiGLU out); weights are the same bf16 values on both sides.
 TOL = {"float32": dict(atol=2e-5, rtol=1e-5), "bfloat16": dict(atol=2e-3, rtol=3e-2)}
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71, 130], "C": [3, 30, 64, 97, 150]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71, 130], "C": [3, 30, 64, 97, 150], "D": [2, 65, 128, 200, 333]}
 
 
 def make_runner(name, dtype, num_pages, page_size=None, max_seqs=8):
@@ -33,7 +33,7 @@ def sequences(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cutting(name, dtype, mode):
     seqs = sequences(name)
