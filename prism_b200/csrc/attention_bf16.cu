@@ -39,7 +39,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                    const int* __restrict__ block_table, int bt_width,
                    const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh,
-                   int nkv, int page_size, int num_pages, int window, float scale_log2,
+                   int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit, int* err) {
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
@@ -77,8 +77,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     auto load_tile = [&](int tile, int stage) {
         __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
-        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, kc, bt, tile * ATT_TILE, lo, hi, page_size, num_pages, nkv, kvh, err);
-        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks + TILE_ELEMS, vc, bt, tile * ATT_TILE, lo, hi, page_size, num_pages, nkv, kvh, err);
+        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
+                                                page_shift, num_pages, nkv, kvh, err);
     };
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) {
@@ -232,7 +232,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                     int out_stride, const __nv_bfloat16* __restrict__ kc,
                     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
                     int bt_width, const int* __restrict__ seg_start, const int* __restrict__ cached_len,
-                    int nh, int nkv, int page_size, int num_pages, int window, float scale_log2, int* err) {
+                    int nh, int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
+                    int* err) {
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
     const int seg = blockIdx.z, h = blockIdx.y;
@@ -260,8 +261,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     }
     auto load_tile = [&](int tile, int stage) {
         __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
-        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, kc, bt, tile * ATT_TILE, lo, hi, page_size, num_pages, nkv, kvh, err);
-        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks + TILE_ELEMS, vc, bt, tile * ATT_TILE, lo, hi, page_size, num_pages, nkv, kvh, err);
+        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
+                                                page_shift, num_pages, nkv, kvh, err);
     };
     load_tile(t0, 0);
     cp_async_commit();
@@ -375,6 +376,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     }
 }
 
+inline int page_shift_of(int page_size) {
+    if (page_size <= 0 || (page_size & (page_size - 1))) return -1;
+    int s = 0;
+    while ((1 << s) < page_size) ++s;
+    return s;
+}
+
 template <int HD> constexpr size_t dec_smem() {
     return (size_t)(16 + DEC_STAGES * 2 * ATT_TILE) * TileRow<HD>::STRIDE * sizeof(__nv_bfloat16);
 }
@@ -393,7 +401,7 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
     dim3 grid(nsplit, nkv, T);
     kern<<<grid, ATT_THREADS, dec_smem<HD>(), stream>>>(q, q_stride, kc, vc, bt, bt_width, positions, tok_seg, nh, nkv,
-                                                        page_size, num_pages, window, scale * 1.4426950408889634f,
+                                                        page_size, page_shift_of(page_size), num_pages, window, scale * 1.4426950408889634f,
                                                         part_o, part_ml, nsplit, err);
     attn_merge_kernel<HD><<<T * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, nsplit, out, out_stride, nh);
     return (int)cudaPeekAtLastError();
@@ -408,7 +416,8 @@ int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pre_smem<HD>());
     dim3 grid((max_q_len + PRE_ROWS - 1) / PRE_ROWS, nh, S);
     kern<<<grid, ATT_THREADS, pre_smem<HD>(), stream>>>(q, q_stride, out, out_stride, kc, vc, bt, bt_width, seg_start,
-                                                        cached_len, nh, nkv, page_size, num_pages, window,
+                                                        cached_len, nh, nkv, page_size, page_shift_of(page_size),
+                                                        num_pages, window,
                                                         scale * 1.4426950408889634f, err);
     return (int)cudaPeekAtLastError();
 }

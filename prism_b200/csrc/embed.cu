@@ -2,6 +2,7 @@
 // stream is float32 in both precisions).  No scaling of the embeddings
 // (andre-fu/prism engine/executor.py:74-75).
 #include "common.cuh"
+#include "vec.cuh"
 
 namespace prism {
 
@@ -17,6 +18,14 @@ __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ 
         return;
     }
     const W* row = table + (size_t)id * H;
+    if (H % 8 == 0) {
+        for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+            float v[8];
+            load8(row + i, v);
+            store8(o + i, v);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
 }
 
@@ -25,7 +34,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ 
 PRISM_EXPORT int prism_embed(const int* ids, const void* table, int table_dtype, float* out,
                              int T, int H, int V, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
-    const int threads = H >= 1024 ? 256 : 128;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (table_dtype == PRISM_DTYPE_BF16)
         prism::embed_kernel<<<T, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V, err);
     else

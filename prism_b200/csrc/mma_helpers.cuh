@@ -48,30 +48,47 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // different 16-byte bank groups, which is what ldmatrix needs.
 template <int HD> struct TileRow { static constexpr int STRIDE = HD + 8; };
 
-// Gather `rows` cache rows (keys first_key .. first_key + rows - 1 of one
-// kv head) into smem[rows][HD + 8].  Keys outside [lo, hi] are zero-filled.
-// A page id outside the pool is reported and the row zero-filled.
+// Gather ROWS cache rows (keys first_key .. first_key + ROWS - 1 of one kv
+// head) of both K and V into ks/vs[ROWS][HD + 8].  A row's offset in the cache
+// is the same for K and V and is computed once.  Keys outside [lo, hi] are
+// zero-filled.  A page id outside the pool is reported and the row
+// zero-filled.  page_shift = log2(page_size) when that is a power of two, else -1.
 template <int HD, int ROWS, int THREADS>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* smem, const __nv_bfloat16* __restrict__ cache,
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
+                                             const __nv_bfloat16* __restrict__ kcache,
+                                             const __nv_bfloat16* __restrict__ vcache,
                                              const int* __restrict__ bt, int first_key, int lo, int hi,
-                                             int page_size, int num_pages, int nkv, int kvh, int* err) {
+                                             int page_size, int page_shift, int num_pages, int nkv, int kvh,
+                                             int* err) {
     constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
-    constexpr int TOTAL = ROWS * CHUNKS;
-    for (int i = threadIdx.x; i < TOTAL; i += THREADS) {
-        const int r = i / CHUNKS, c = i % CHUNKS;
+    constexpr int ROW_STEP = THREADS / CHUNKS;
+    static_assert(THREADS % CHUNKS == 0 && ROWS % ROW_STEP == 0, "tile shape");
+    const int c = threadIdx.x % CHUNKS;
+    const size_t row_elems = (size_t)nkv * HD;
+    const size_t head_off = (size_t)kvh * HD + c * 8;
+#pragma unroll
+    for (int r = threadIdx.x / CHUNKS; r < ROWS; r += ROW_STEP) {
         const int key = first_key + r;
         bool valid = key >= lo && key <= hi;
-        const __nv_bfloat16* src = cache;
+        size_t off = 0;
         if (valid) {
-            const int page = bt[key / page_size];
+            int page, in_page;
+            if (page_shift >= 0) {
+                page = bt[key >> page_shift];
+                in_page = key & (page_size - 1);
+            } else {
+                page = bt[key / page_size];
+                in_page = key % page_size;
+            }
             if (page < 0 || page >= num_pages) {
                 report_error(err, PRISM_ERR_PAGE_RANGE);
                 valid = false;
             } else {
-                src = cache + (((size_t)page * page_size + key % page_size) * nkv + kvh) * HD + c * 8;
+                off = ((size_t)page * page_size + in_page) * row_elems + head_off;
             }
         }
-        cp_async16(smem + r * TileRow<HD>::STRIDE + c * 8, src, valid);
+        cp_async16(ks + r * TileRow<HD>::STRIDE + c * 8, kcache + off, valid);
+        cp_async16(vs + r * TileRow<HD>::STRIDE + c * 8, vcache + off, valid);
     }
 }
 

@@ -11,6 +11,7 @@
 // position % P (the append that flash_attn_with_kvcache does at
 // executor.py:119-120).  Cache layout: [page, P, nkv, hd].
 #include "common.cuh"
+#include "vec.cuh"
 
 namespace prism {
 
@@ -79,18 +80,126 @@ __global__ void rope_kv_kernel(T* __restrict__ q, T* __restrict__ k, const T* __
         for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) vc[slot + i] = vrow[i];
 }
 
+// cos/sin of every (token, pair) of a step, computed once and shared by all
+// layers and heads: table[t, j] = (cos, sin)(position[t] * inv_freq[j]), float32.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  int half, int T, float2* __restrict__ table) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * half) return;
+    float s, c;
+    sincosf((float)positions[i / half] * inv_freq[i % half], &s, &c);
+    table[i] = make_float2(c, s);
+}
+
+// Vector version: head_dim % 8 == 0 and rotary_dim % 16 == 0; cos/sin come from
+// the table.  A thread rotates 8 neighbouring pairs (two 16-byte accesses for
+// bf16), or copies 8 unrotated dims.
+template <typename T>
+__global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T* __restrict__ v,
+                                   int row_stride, const int* __restrict__ positions,
+                                   const int* __restrict__ tok_seg, const float2* __restrict__ table,
+                                   int rd, T* __restrict__ kc, T* __restrict__ vc,
+                                   const int* __restrict__ block_table, int bt_width, int page_size,
+                                   int num_pages, int nh, int nkv, int hd, int max_pos, int* err) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0) report_error(err, PRISM_ERR_POSITION_RANGE);
+        return;
+    }
+    size_t slot = 0;
+    bool store = kc != nullptr;
+    if (store) {
+        const int page = block_table[(size_t)tok_seg[t] * bt_width + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
+            store = false;
+        } else {
+            slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
+        }
+    }
+    const int half = rd / 2;
+    const int rot_chunks = half / 8;                   // chunks of 8 rotated pairs per head
+    const int pass_chunks = (hd - rd) / 8;             // chunks of 8 unrotated dims per head
+    const int per_k = rot_chunks + pass_chunks;
+    const int n_q = nh * rot_chunks, n_k = nkv * per_k, n_v = nkv * (hd / 8);
+    const float2* tab = table + (size_t)t * half;
+    for (int i = threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x) {
+        if (i < n_q + n_k) {
+            const bool is_q = i < n_q;
+            const int ii = is_q ? i : i - n_q;
+            const int per = is_q ? rot_chunks : per_k;
+            const int h = ii / per, c = ii % per;
+            T* p = (is_q ? q : k) + (size_t)t * row_stride + h * hd;
+            if (c < rot_chunks) {
+                const int j = c * 8;
+                float x1[8], x2[8], y1[8], y2[8];
+                load8(p + j, x1);
+                load8(p + j + half, x2);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float2 cs = tab[j + e];
+                    y1[e] = x1[e] * cs.x - x2[e] * cs.y;
+                    y2[e] = x2[e] * cs.x + x1[e] * cs.y;
+                }
+                store8(p + j, y1);
+                store8(p + j + half, y2);
+                if (!is_q && store) {
+                    store8(kc + slot + h * hd + j, y1);
+                    store8(kc + slot + h * hd + j + half, y2);
+                }
+            } else if (store) {                          // only k has these items
+                const int d = rd + (c - rot_chunks) * 8;
+                float x[8];
+                load8(p + d, x);
+                store8(kc + slot + h * hd + d, x);
+            }
+        } else if (store) {
+            const int d = (i - n_q - n_k) * 8;
+            float x[8];
+            load8(v + (size_t)t * row_stride + d, x);
+            store8(vc + slot + d, x);
+        }
+    }
+}
+
 }  // namespace prism
 
 // inv_freq may be null with rotary_dim 0: no rotation, only the cache store.
 // kc/vc may be null: only the rotation.
+PRISM_EXPORT int prism_rope_table(const int* positions, const float* inv_freq, int half, int T,
+                                  float* table, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return 0;
+    const int n = T * half;
+    prism::rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, half, T, (float2*)table);
+    return (int)cudaPeekAtLastError();
+}
+
+// `table` (optional): float2 [T, rotary_dim / 2] from prism_rope_table; with it, and with
+// head_dim % 8 == 0 and rotary_dim % 16 == 0, the vector kernel runs.
 PRISM_EXPORT int prism_rope_kv_write(void* q, void* k, const void* v, int dtype, int row_stride,
                                      const int* positions, const int* tok_seg,
-                                     const float* inv_freq, int rotary_dim, void* kc, void* vc,
+                                     const float* inv_freq, const float* table, int rotary_dim, void* kc, void* vc,
                                      const int* block_table, int bt_width, int page_size,
                                      int num_pages, int T, int nh, int nkv, int hd, int max_pos,
                                      int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+    if (table != nullptr && hd % 8 == 0 && rotary_dim % 16 == 0 && row_stride % 8 == 0) {
+        const int items = (nh + nkv) * (hd / 2 / 8) + nkv * (hd / 8) + nkv * ((hd - rotary_dim) / 8);
+        const int vthreads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+        if (dtype == PRISM_DTYPE_BF16)
+            prism::rope_kv_vec_kernel<__nv_bfloat16><<<T, vthreads, 0, stream>>>(
+                (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, positions,
+                tok_seg, (const float2*)table, rotary_dim, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
+                block_table, bt_width, page_size, num_pages, nh, nkv, hd, max_pos, err);
+        else
+            prism::rope_kv_vec_kernel<float><<<T, vthreads, 0, stream>>>(
+                (float*)q, (float*)k, (const float*)v, row_stride, positions, tok_seg,
+                (const float2*)table, rotary_dim, (float*)kc, (float*)vc, block_table, bt_width,
+                page_size, num_pages, nh, nkv, hd, max_pos, err);
+        return (int)cudaPeekAtLastError();
+    }
     const int threads = 128;
     if (dtype == PRISM_DTYPE_BF16)
         prism::rope_kv_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(

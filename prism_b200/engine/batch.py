@@ -70,6 +70,7 @@ class StepContext:
         self.host = host                       # host copies of the arrays (None inside a captured graph)
         self.max_q_len, self.max_kv_len = int(max_q_len), int(max_kv_len)
         self.decode_only = max_q_len == 1
+        self.scratch = {}                      # per-step values shared by parts (e.g. the rotary table)
         v = lambda n: layout.view(dev_buf, n)
         self.token_ids, self.positions, self.tok_seg = v("token_ids"), v("positions"), v("tok_seg")
         self.seg_start, self.cached_len, self.q_len = v("seg_start"), v("cached_len"), v("q_len")

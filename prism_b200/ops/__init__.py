@@ -79,7 +79,8 @@ _p, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlo
 class _Sig:
     prism_embed = [_p, _p, _i, _p, _i, _i, _i, _p, _p]
     prism_add_rmsnorm = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _p, _i, _i, _p]
-    prism_rope_kv_write = [_p, _p, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i,
+    prism_rope_table = [_p, _p, _i, _i, _p, _p]
+    prism_rope_kv_write = [_p, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i,
                            _i, _i, _p, _p]
     prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                _i, _f, _p, _p]
@@ -204,14 +205,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return torch.addmm(b, x, w.t(), out=out)
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor):
+    """``out[t, j] = (cos, sin)(positions[t] * inv_freq[j])`` in float32, shared
+    by every layer and head of a step."""
+    _cuda(positions, inv_freq, out)
+    T, half = positions.shape[0], inv_freq.shape[0]
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, half, 2)
+    _check(lib().prism_rope_table(_ptr(positions), _ptr(inv_freq), half, T, _ptr(out), _stream()), "rope_table")
+
+
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor,
                   tok_seg: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                   block_table: Optional[torch.Tensor], num_pages: int, max_pos: int,
-                  err: torch.Tensor):
+                  err: torch.Tensor, table: Optional[torch.Tensor] = None):
     """Rotate ``q [T, nh, hd]`` and ``k [T, nkv, hd]`` in place (views of one
     row-strided buffer) and store k, v at their positions in the paged cache
-    ``[pages, P, nkv, hd]``.  ``k_cache`` None: rotate only."""
+    ``[pages, P, nkv, hd]``.  ``k_cache`` None: rotate only.  ``table``: the
+    step's cos/sin table from ``rope_table`` (lets the vector kernel run)."""
     _cuda(q, k, v, positions, tok_seg, inv_freq, k_cache, v_cache, block_table)
     T, nh, hd = q.shape
     nkv = k.shape[1]
@@ -226,8 +237,12 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: 
         P, W = k_cache.shape[1], block_table.shape[1]
     if inv_freq is not None:
         assert inv_freq.dtype == torch.float32 and inv_freq.shape[0] * 2 == rotary_dim
+    if T == 1:
+        rs = 0                  # a single row: its stride is never used
+    if table is not None:
+        assert table.dtype == torch.float32 and table.shape == (T, rotary_dim // 2, 2)
     _check(lib().prism_rope_kv_write(_ptr(q), _ptr(k), _ptr(v), _dt(q), rs, _ptr(positions),
-                                     _ptr(tok_seg), _ptr(inv_freq), rotary_dim, _ptr(k_cache),
+                                     _ptr(tok_seg), _ptr(inv_freq), _ptr(table), rotary_dim, _ptr(k_cache),
                                      _ptr(v_cache), _ptr(block_table), W, P, num_pages, T, nh, nkv,
                                      hd, max_pos, _ptr(err), _stream()), "rope_kv_write")
 

@@ -199,7 +199,8 @@ def test_swiglu(T, I, dtype):
 
 @pytest.mark.parametrize("nh,nkv,hd,rd,P", [(5, 1, 48, 48, 8), (28, 4, 128, 128, 256), (6, 3, 80, 32, 16), (2, 2, 16, 0, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_kv_write(nh, nkv, hd, rd, P, dtype):
+@pytest.mark.parametrize("use_table", [False, True])
+def test_rope_kv_write(nh, nkv, hd, rd, P, dtype, use_table):
     ops = _ops()
     T, S, W = 23, 3, 40
     pages = S * W
@@ -222,7 +223,12 @@ def test_rope_kv_write(nh, nkv, hd, rd, P, dtype):
     theta = 1e6
     inv = (1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))).to(DEV) if rd else None
     err = _err()
-    ops.rope_kv_write(q, k, v, positions.to(DEV), tok_seg.to(DEV), inv, rd, kc, vc, bt.to(DEV), pages, 10 ** 6, err)
+    table = None
+    if use_table and rd:
+        table = torch.empty(T, rd // 2, 2, dtype=torch.float32, device=DEV)
+        ops.rope_table(positions.to(DEV), inv, table)
+    ops.rope_kv_write(q, k, v, positions.to(DEV), tok_seg.to(DEV), inv, rd, kc, vc, bt.to(DEV), pages, 10 ** 6, err,
+                      table=table)
     assert int(err) == 0
     bq = before[:, :nh * hd].view(T, nh, hd).float()
     bk = before[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd).float()
