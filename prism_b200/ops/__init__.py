@@ -92,6 +92,8 @@ class _Sig:
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
+    prism_gemv_bf16_supported = [_i, _i, _i]
+    prism_gemv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]
 
 
 def _stream() -> int:
@@ -166,6 +168,32 @@ def sgemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: t
                                 _stream()), "sgemm")
 
 
+USE_GEMV = os.environ.get("PRISM_GEMV", "1") != "0"
+GEMV_MAX_M = 32
+EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+
+
+def gemv_supported(M: int, N: int, K: int) -> bool:
+    return USE_GEMV and bool(lib().prism_gemv_bf16_supported(M, N, K))
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epi: int = EPI_BF16):
+    """Weight-streaming product for a few tokens: ``out = x @ w.T (+ bias)`` in
+    bf16 (``EPI_BF16``) or float32 (``EPI_F32``); or, with ``w`` the fused
+    ``[2I, K]`` gate/up weight, ``out[M, I] = silu(x @ gate.T) * (x @ up.T)``
+    (``EPI_SWIGLU``)."""
+    _cuda(x, w, bias, out)
+    M, K = x.shape
+    N = out.shape[1]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == M
+    assert w.shape[0] == (2 * N if epi == EPI_SWIGLU else N)
+    assert out.dtype == (torch.float32 if epi == EPI_F32 else torch.bfloat16)
+    _check(lib().prism_gemv_bf16(_ptr(w), w.stride(0), _ptr(x), x.stride(0) if M > 1 else K, _ptr(bias),
+                                 F32 if bias is None else _dt(bias), _ptr(out), out.stride(0) if M > 1 else N,
+                                 M, N, K, epi, _stream()), "gemv_bf16")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x @ w.T + bias`` with ``w`` in the ``[out, in]`` layout of the model
@@ -188,6 +216,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             out.copy_(o32)
             return out
         return o32.to(want)
+    if want in (torch.float32, torch.bfloat16) and M <= GEMV_MAX_M and x.stride(-1) == 1 \
+            and (out is None or out.stride(-1) == 1) and gemv_supported(M, N, x.shape[1]) \
+            and (M == 1 or x.stride(0) % 8 == 0):
+        if out is None or out.dtype != want:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        gemv(x, w, bias, out, EPI_F32 if want == torch.float32 else EPI_BF16)
+        return out
     # bf16 x bf16, library product with float32 accumulation
     if want == torch.float32:
         res = torch.mm(x, w.t(), out_dtype=torch.float32)
@@ -367,6 +402,12 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
 
 def feed_forward_swiglu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor):
     """``down(silu(gate(x)) * up(x))`` with the fused gate/up weight."""
+    M, I = x.shape[0], gate_up_w.shape[0] // 2
+    if x.dtype == torch.bfloat16 and gate_up_w.dtype == torch.bfloat16 and M <= GEMV_MAX_M \
+            and gemv_supported(M, I, x.shape[1]) and (M == 1 or x.stride(0) % 8 == 0):
+        act = ctx.alloc((M, I), x.dtype)
+        gemv(x, gate_up_w, None, act, EPI_SWIGLU)        # gate/up product with the SwiGLU in its epilogue
+        return linear(act, down_w)
     gu = linear(x, gate_up_w)
     act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
     swiglu(gu, act)

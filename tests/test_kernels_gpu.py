@@ -184,6 +184,32 @@ def test_linear_bf16(M, N, K):
     assert out_mixed.dtype == torch.bfloat16 and torch.allclose(out_mixed.float(), ref, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 23, 32])
+@pytest.mark.parametrize("N,K", [(4608, 3584), (3584, 18944), (100, 96), (1000, 40), (17, 3000), (152064 // 16 + 3, 512)])
+def test_gemv_bf16(M, N, K):
+    """The weight-streaming small-M product alone: bf16 and float32 outputs with
+    bias, and the paired-SwiGLU epilogue, against float32 references."""
+    ops = _ops()
+    x = _rand((M, K), torch.bfloat16, 30)
+    w = _rand((N, K), torch.bfloat16, 31, 0.05)
+    b = _rand((N,), torch.bfloat16, 32)
+    ref = x.float() @ w.float().T + b.float()
+    scale = float(ref.abs().max())
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemv(x, w, b, out, ops.EPI_BF16)
+    assert torch.allclose(out.float(), ref, atol=8e-3 * scale, rtol=1e-2)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemv(x, w, None, out32, ops.EPI_F32)
+    assert torch.allclose(out32, ref - b.float(), atol=2e-3 * scale, rtol=2e-3)
+    if N % 2 == 0:
+        I = N // 2
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemv(x, w, None, act, ops.EPI_SWIGLU)
+        g, u = (ref - b.float())[:, :I], (ref - b.float())[:, I:]
+        r = g * torch.sigmoid(g) * u
+        assert torch.allclose(act.float(), r, atol=1e-2 * float(r.abs().max()) + 1e-3, rtol=2e-2)
+
+
 @pytest.mark.parametrize("T,I", [(3, 100), (40, 18944)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu(T, I, dtype):
