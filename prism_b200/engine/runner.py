@@ -145,19 +145,23 @@ class ModelRunner:
         host = pack_batch(layout, [0] * B, [0] * B, list(range(B)), list(range(B + 1)), [0] * B, [1] * B,
                           [self.cache.max_seqs] * B, list(range(B)), pad_rows, self.pad_page)
         dev.copy_(host)
-        ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions, None,
-                          1, self.max_seq_len)
-        views = self.storage.views(ctx.block_tables, ctx.state_slots, None)
+        def fresh_ctx():
+            # every run gets its own context: values parts keep for the length of a step (the
+            # rotary table) must be produced inside the capture, in the graph's own memory
+            c = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions, None,
+                            1, self.max_seq_len)
+            return c, self.storage.views(c.block_tables, c.state_slots, None)
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):                       # warm-up: lazy library set-up happens outside capture
-                self.model.forward(ctx, views)
+                self.model.forward(*fresh_ctx())
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         from .. import ops
         before = ops.launch_count
+        ctx, views = fresh_ctx()
         with torch.cuda.graph(graph, stream=stream):
             out = self.model.forward(ctx, views)
         torch.cuda.synchronize(self.device)
