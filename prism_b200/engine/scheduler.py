@@ -183,7 +183,7 @@ class Scheduler:
             segs.append(Segment(req.id, toks, [n - 1] if last else []))
             if last:
                 sampled.append(req)
-            if n == 1 and req.remaining == 1:
+            if n == 1 and req.num_computed >= len(req.prompt_tokens):
                 self.stats.decode_tokens += 1
             else:
                 self.stats.prefill_tokens += n

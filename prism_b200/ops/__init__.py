@@ -169,6 +169,9 @@ def sgemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: t
 
 
 USE_GEMV = os.environ.get("PRISM_GEMV", "1") != "0"
+# the plain (bias) epilogue is slower than the library product at most decode shapes on B200 and is
+# opt-in; the paired-SwiGLU epilogue saves the [M, 2I] round trip and a launch and is the default
+USE_GEMV_PLAIN = os.environ.get("PRISM_GEMV_PLAIN", "0") == "1"
 GEMV_MAX_M = 32
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 
@@ -216,7 +219,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             out.copy_(o32)
             return out
         return o32.to(want)
-    if want in (torch.float32, torch.bfloat16) and M <= GEMV_MAX_M and x.stride(-1) == 1 \
+    if USE_GEMV_PLAIN and want in (torch.float32, torch.bfloat16) and M <= GEMV_MAX_M and x.stride(-1) == 1 \
             and (out is None or out.stride(-1) == 1) and gemv_supported(M, N, x.shape[1]) \
             and (M == 1 or x.stride(0) % 8 == 0):
         if out is None or out.dtype != want:
@@ -376,7 +379,9 @@ def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> i
     on every SM, at most one per 64-key tile."""
     span = min(max_kv_len, window + 64) if window else max_kv_len
     tiles = max(1, (span + 63) // 64)
-    return max(1, min(tiles, 64, -(-2 * NUM_SMS // max(1, T * nkv))))
+    fill = (2 * NUM_SMS) // max(1, T * nkv)          # one wave of two CTAs per SM, not a little more
+    balance = -(-tiles // 8)                          # at most ~8 tiles per CTA so that SMs finish together
+    return max(1, min(tiles, 64, max(fill, balance)))
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[int], scale: float):

@@ -97,11 +97,18 @@ def rotate_half(x: torch.Tensor) -> torch.Tensor:
     return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
 
 
-def apply_rope(x: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float):
+    """``cos``, ``sin`` of the angles, each [T, hd/2] float32 (engine/executor.py:53-54
+    without the rounding to bf16 that the executor applies there)."""
+    ang = rope_angles(positions, head_dim, theta)
+    return ang.cos(), ang.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """``x*cos + rotate_half(x)*sin`` with cos/sin repeated over both halves
-    (engine/executor.py:53-57,117-118).  x: [T, heads, hd]."""
-    cos = torch.cat([angles.cos(), angles.cos()], dim=-1)[:, None, :]
-    sin = torch.cat([angles.sin(), angles.sin()], dim=-1)[:, None, :]
+    (engine/executor.py:55-57,117-118).  x: [T, heads, hd]; cos, sin: [T, hd/2]."""
+    cos = torch.cat([cos, cos], dim=-1)[:, None, :]
+    sin = torch.cat([sin, sin], dim=-1)[:, None, :]
     return x * cos + rotate_half(x) * sin
 
 
@@ -131,7 +138,7 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate * torch.sigmoid(gate) * up
 
 
-def decoder_layer(x, t, i, cfg, positions):
+def decoder_layer(x, t, i, cfg, positions, cos_sin=None):
     """One pre-norm block (engine/executor.py:106-127): norm, fused qkv with
     bias, rope on q and k, attention, o-projection + residual, norm, gate/up,
     SwiGLU, down-projection + residual."""
@@ -147,9 +154,9 @@ def decoder_layer(x, t, i, cfg, positions):
         q = q + t[p + "self_attn.q_proj.bias"]
         k = k + t[p + "self_attn.k_proj.bias"]
         v = v + t[p + "self_attn.v_proj.bias"]
-    ang = rope_angles(positions, hd, cfg.get("rope_theta", 10000.0))
-    q = apply_rope(q.view(T, nh, hd), ang)
-    k = apply_rope(k.view(T, nkv, hd), ang)
+    cos, sin = cos_sin if cos_sin is not None else rope_cos_sin(positions, hd, cfg.get("rope_theta", 10000.0))
+    q = apply_rope(q.view(T, nh, hd), cos, sin)
+    k = apply_rope(k.view(T, nkv, hd), cos, sin)
     a = attention(q, k, v.view(T, nkv, hd), layer_window(cfg, i))
     x = x + a.reshape(T, nh * hd) @ t[p + "self_attn.o_proj.weight"].T
     h = rms_norm(x, t[p + "post_attention_layernorm.weight"], eps)
@@ -159,14 +166,15 @@ def decoder_layer(x, t, i, cfg, positions):
     return x
 
 
-def forward(cfg: dict, t: dict, tokens) -> torch.Tensor:
+def forward(cfg: dict, t: dict, tokens, cos_sin=None) -> torch.Tensor:
     """Logits at every position of one whole sequence, float32 [T, V]
-    (engine/executor.py:99-130, with the head applied to all rows)."""
+    (engine/executor.py:99-130, with the head applied to all rows).
+    ``cos_sin``: rotary tables to use instead of the float32 ones."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(tokens.shape[0])
     x = embed(tokens, t["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, t, i, cfg, positions)
+        x = decoder_layer(x, t, i, cfg, positions, cos_sin)
     h = rms_norm(x, t["model.norm.weight"], cfg.get("rms_norm_eps", 1e-6))
     return h @ t["lm_head.weight"].T
 

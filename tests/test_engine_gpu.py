@@ -1,0 +1,163 @@
+"""Generation through the entry point, decode graphs, sampling, preemption,
+long decoding and the replay program, against the plain implementation (GPU)."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (P, TINY, compare_with_plain, model_folder, plain_logits, plain_model, random_tokens,
+                     trace_budget, trace_mixed, trace_tail)
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def engine(name, dtype, **kw):
+    from prism_b200 import Engine, EngineConfig, SchedulerConfig
+    sched = SchedulerConfig(**{k: kw.pop(k) for k in ("max_batch_tokens", "max_num_seqs", "prefill_chunk") if k in kw})
+    ec = EngineConfig(kv_page_size=kw.pop("page_size", TINY[name][2]), num_pages=kw.pop("num_pages", 64),
+                      use_cuda_graph=kw.pop("graph", False), graph_batch_sizes=(1, 2, 4), scheduler=sched, **kw)
+    return Engine(model_folder(name), ec, dtype=dtype)
+
+
+def near_greedy(name, prompt, tokens, slack):
+    """Every generated token is the plain model's best token given the same
+    history, up to a logit gap of ``slack`` (bf16 may flip a near-tie)."""
+    for i, tok in enumerate(tokens):
+        lg = plain_logits(name, list(prompt) + list(tokens[:i]))[-1]
+        assert float(lg.max() - lg[tok]) <= slack * float(lg.abs().max()) + 1e-6, (i, tok)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_greedy_generation_matches_the_plain_model(name):
+    from prism_b200 import SamplingParams
+    cfg, t = plain_model(name)
+    vocab = TINY[name][0]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 10 + n) for n in (5, 17, 33)]
+    want = [P.generate(cfg, t, p, 8) for p in prompts]
+    got = engine(name, "float32").generate(prompts, SamplingParams(max_new_tokens=8))
+    assert [r.token_ids for r in got] == want and all(r.finish_reason == "length" for r in got)
+    got16 = engine(name, "bfloat16").generate(prompts, SamplingParams(max_new_tokens=8))
+    for p, r in zip(prompts, got16):
+        near_greedy(name, p, r.token_ids, 0.03)
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16"), ("A", "bfloat16")])
+def test_decode_graphs_give_the_eager_result(name, dtype):
+    """Chunked prefill mixed with decode, then decode steps replayed from captured
+    graphs (buckets 1, 2, 4 with padding rows): same tokens as without graphs."""
+    from prism_b200 import SamplingParams
+    vocab = TINY[name][0]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 70 + n) for n in (1, 9, 40)]
+    sp = [SamplingParams(max_new_tokens=n) for n in (12, 7, 9)]
+    a = engine(name, dtype, graph=False, prefill_chunk=16, max_batch_tokens=24).generate(prompts, sp)
+    eg = engine(name, dtype, graph=True, prefill_chunk=16, max_batch_tokens=24)
+    b = eg.generate(prompts, sp)
+    assert [r.token_ids for r in a] == [r.token_ids for r in b]
+    assert eg.runner.graph_kernel_launches > 0 and set(eg.runner._graphs) <= {1, 2, 4}
+    b2 = eg.generate(prompts, sp)                       # the captured graphs again, other pages
+    assert [r.token_ids for r in b2] == [r.token_ids for r in b]
+
+
+def test_temperature_sampling_matches_the_plain_sampler():
+    """Config B's workload: prompts 1/9/40/71, prefill in portions of 16 mixed with
+    decode, 6 tokens at temperature 0.7 from seed 4 - the same draws as the plain
+    loop, whose uniform numbers are keyed by (seed, request, step)."""
+    from prism_b200 import SamplingParams
+    cfg, t = plain_model("B")
+    prompts = [random_tokens(320, n, 3 + n) for n in (1, 9, 40, 71)]
+    eng = engine("B", "float32", prefill_chunk=16, max_batch_tokens=40)
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=6, temperature=0.7, seed=4))
+    for i, (p, r) in enumerate(zip(prompts, got)):
+        assert r.token_ids == P.generate(cfg, t, p, 6, temperature=0.7, seed=4, request_index=i)
+    assert len({tuple(r.token_ids) for r in got}) > 1
+
+
+def test_preemption_recomputes_and_keeps_the_tokens():
+    """A pool too small for all running requests to reach their ends: requests
+    are preempted and recomputed, and the tokens are those of an ample pool."""
+    from prism_b200 import SamplingParams
+    prompts = [random_tokens(256, n, 90 + n) for n in (20, 14, 9)]
+    sp = SamplingParams(max_new_tokens=24)
+    ample = engine("A", "float32", num_pages=64).generate(prompts, sp)
+    tight = engine("A", "float32", num_pages=6, page_size=8)     # 48 tokens of cache for 44 + 38 + 33
+    got = tight.generate(prompts, sp)
+    assert tight.stats.preemptions > 0 and sum(r.num_preemptions for r in got) == tight.stats.preemptions
+    assert [r.token_ids for r in got] == [r.token_ids for r in ample]
+    assert tight.cache.pages_in_use() == 0
+    cfg, t = plain_model("A")
+    assert got[0].token_ids == P.generate(cfg, t, prompts[0], 24)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(dtype):
+    """One token a step from the first position on, for 300 steps across many
+    pages (and far beyond the window of config D's upper layer)."""
+    from test_replay_gpu import TOL, make_runner
+    from helpers import run_trace
+    seq = random_tokens(301, 300, 5)
+    steps = [dict(step=i, entries=[dict(id="r", tokens=[tok], want=[0])], end=["r"] if i == 299 else [])
+             for i, tok in enumerate(seq)]
+    runner = make_runner("D", dtype, num_pages=10)        # 10 pages of 32
+    got = run_trace(runner, steps)
+    worst, where = compare_with_plain("D", {"r": seq}, got, **TOL[dtype])
+    assert len(got) == 300
+
+
+def test_decode_many_requests_with_graphs_and_padding_rows():
+    """Up to 7 requests decoding in a bucket of 8: padded rows must not disturb
+    anything (they write to the scratch page)."""
+    from prism_b200 import Engine, EngineConfig, SamplingParams, SchedulerConfig
+    cfg, t = plain_model("A")
+    ec = EngineConfig(kv_page_size=16, num_pages=40, use_cuda_graph=True, graph_batch_sizes=(8,),
+                      scheduler=SchedulerConfig(max_num_seqs=8))
+    eng = Engine(model_folder("A"), ec, dtype="float32")
+    prompts = [random_tokens(256, 3 + 2 * i, 200 + i) for i in range(7)]
+    sp = [SamplingParams(max_new_tokens=4 + i) for i in range(7)]
+    got = eng.generate(prompts, sp)
+    for p, s, r in zip(prompts, sp, got):
+        assert r.token_ids == P.generate(cfg, t, p, s.max_new_tokens)
+
+
+def test_bad_token_id_is_reported_not_faulted():
+    from prism_b200 import SamplingParams
+    from prism_b200.engine.runner import DeviceError
+    eng = engine("A", "float32")
+    with pytest.raises(DeviceError, match="token id"):
+        eng.generate([[1, 2, 999]], SamplingParams(max_new_tokens=2))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """bin/trace_run as a user runs it: JSON steps on standard input, <step>.f32
+    files out, `done <step>` after each step; pool sized by --max-tokens so that
+    pages are used again."""
+    name = "B"
+    seqs = {f"q{i}": random_tokens(320, n, 300 + i) for i, n in enumerate([70, 33, 90, 12, 64])}
+    steps = trace_mixed(seqs, seed=11)
+    budget = trace_budget(steps, 64)
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folder(name),
+                           "--dtype", dtype, "--out", str(out), "--max-tokens", str(budget), "--page-size", "16"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    got, fed = {}, {}
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        data = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(n_want, 320)
+        r = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                got[(e["id"], fed.get(e["id"], 0) + w)] = torch.from_numpy(data[r].copy())
+                r += 1
+            fed[e["id"]] = fed.get(e["id"], 0) + len(e["tokens"])
+    from test_replay_gpu import TOL
+    compare_with_plain(name, seqs, got, **TOL[dtype])
+    assert len(got) == sum(len(s) for s in seqs.values())
