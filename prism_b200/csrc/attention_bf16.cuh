@@ -1,0 +1,428 @@
+// bf16 paged causal grouped-query attention on tensor cores, two kernels:
+//
+//  * decode: one new token per request.  A CTA takes one (token, kv head,
+//    split of the keys); the nh/nkv query heads of that kv head form the rows
+//    of one 16-row MMA tile, so a K/V tile is read once for all of them.  Four
+//    warps each take 16 of a tile's 64 keys; partial (max, sum, output) of the
+//    warps and then of the splits are merged by a second small kernel.
+//  * prefill / portions: a CTA takes 64 query rows of one head of one
+//    segment; keys come from the request's pages (earlier portions and this
+//    one), causal with the portion's offset: the row at position p sees keys
+//    <= p (and > p - window).
+//
+// Both compute what flash_attn_with_kvcache(causal=True) computes in
+// andre-fu/prism (engine/executor.py:119-120,151-153): scale hd^-1/2, scores,
+// running max and sum and output accumulation in float32, probabilities
+// rounded to bf16 for the PV product.  K/V tiles of 64 keys are gathered
+// through the block table with 16-byte cp.async (any page size) into padded
+// shared memory, 3 stages deep (decode) or double-buffered (prefill).
+#pragma once
+
+#include "mma_helpers.cuh"
+
+namespace prism {
+
+constexpr int ATT_TILE = 64;       // keys per tile
+constexpr int ATT_THREADS = 128;   // 4 warps
+constexpr int DEC_STAGES = 3;
+constexpr int PRE_STAGES = 2;
+constexpr int PRE_ROWS = 64;       // query rows per CTA
+
+__device__ __forceinline__ float exp2_guard(float x, float m) {   // exp2(x - m), 0 when x is -inf
+    return x == -INFINITY ? 0.f : exp2f(x - m);
+}
+
+// ---------------------------------------------------------------------------
+// decode
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
+                   const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                   const int* __restrict__ block_table, int bt_width,
+                   const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh,
+                   int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit, int* err) {
+    constexpr int STRIDE = TileRow<HD>::STRIDE;
+    constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][STRIDE]
+    __nv_bfloat16* KV = Qs + 16 * STRIDE;                            // [stage][K|V][64][STRIDE]
+
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = nh / nkv;
+    const int pos = positions[t];
+    const int* bt = block_table + (size_t)tok_seg[t] * bt_width;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int hi = pos;
+    const int first_tile = lo / ATT_TILE, ntiles = hi / ATT_TILE - first_tile + 1;
+    const int per_split = (ntiles + nsplit - 1) / nsplit;
+    const int t0 = first_tile + split * per_split;
+    const int t1 = min(t0 + per_split, first_tile + ntiles);
+
+    float* po = part_o + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * HD;   // + row * nsplit * HD
+    float* pml = part_ml + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * 2;
+    if (t0 >= t1) {           // nothing for this split: an empty partial
+        for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * nsplit * HD + i % HD] = 0.f;
+        for (int r = tid; r < g; r += ATT_THREADS) {
+            pml[(size_t)r * nsplit * 2] = -INFINITY;
+            pml[(size_t)r * nsplit * 2 + 1] = 0.f;
+        }
+        return;
+    }
+
+    // Q rows of this kv head's group (rows >= g are zero)
+    for (int i = tid; i < 16 * (HD / 8); i += ATT_THREADS) {
+        const int r = i / (HD / 8), c = i % (HD / 8);
+        cp_async16(Qs + r * STRIDE + c * 8, q + (size_t)t * q_stride + ((size_t)kvh * g + (r < g ? r : 0)) * HD + c * 8, r < g);
+    }
+    auto load_tile = [&](int tile, int stage) {
+        __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
+        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
+                                                page_shift, num_pages, nkv, kvh, err);
+    };
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (t0 + s < t1) load_tile(t0 + s, s);
+        cp_async_commit();
+    }
+
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int mat = lane >> 3, lr = lane & 7;
+
+    for (int tile = t0; tile < t1; ++tile) {
+        const int it = tile - t0;
+        if (tile + DEC_STAGES - 1 < t1) load_tile(tile + DEC_STAGES - 1, (it + DEC_STAGES - 1) % DEC_STAGES);
+        cp_async_commit();
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldmatrix_x4(qf[ks], Qs + (lr + (mat & 1) * 8) * STRIDE + ks * 16 + (mat >> 1) * 8);
+        }
+        const __nv_bfloat16* Ks = KV + (size_t)(it % DEC_STAGES) * 2 * TILE_ELEMS + warp * 16 * STRIDE;
+        const __nv_bfloat16* Vs = Ks + TILE_ELEMS;
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t b[4];
+            ldmatrix_x4(b, Ks + ((mat >> 1) * 8 + lr) * STRIDE + ks * 16 + (mat & 1) * 8);
+            mma_bf16_16816(s[0], qf[ks], b[0], b[1]);
+            mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
+        }
+        // mask, scale, online softmax over this warp's 16 keys (rows lane/4 and lane/4 + 8)
+        const int key0 = tile * ATT_TILE + warp * 16 + (lane & 3) * 2;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nt * 8 + (e & 1);
+                const float v = (key >= lo && key <= hi) ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float corr[2], mu[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            mu[r] = m_new == -INFINITY ? 0.f : m_new;
+            corr[r] = exp2_guard(m_run[r], mu[r]);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = exp2_guard(s[nt][e], mu[e >> 1]);
+                s[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+        uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                          pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+        for (int j = 0; j < HD / 16; ++j) {
+            o[2 * j][0] *= corr[0]; o[2 * j][1] *= corr[0]; o[2 * j][2] *= corr[1]; o[2 * j][3] *= corr[1];
+            o[2 * j + 1][0] *= corr[0]; o[2 * j + 1][1] *= corr[0]; o[2 * j + 1][2] *= corr[1]; o[2 * j + 1][3] *= corr[1];
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, Vs + ((mat & 1) * 8 + lr) * STRIDE + j * 16 + (mat >> 1) * 8);
+            mma_bf16_16816(o[2 * j], pa, b[0], b[1]);
+            mma_bf16_16816(o[2 * j + 1], pa, b[2], b[3]);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    // merge the four warps' partials through shared memory
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* red_o = reinterpret_cast<float*>(KV);                 // [4][16][HD]
+    float* red_m = red_o + 4 * 16 * HD;                          // [4][16]
+    float* red_l = red_m + 4 * 16;                               // [4][16]
+    const int r0 = lane >> 2;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+        const int d = nt * 8 + (lane & 3) * 2;
+        float* w0 = red_o + ((size_t)warp * 16 + r0) * HD + d;
+        w0[0] = o[nt][0]; w0[1] = o[nt][1];
+        w0[8 * HD] = o[nt][2]; w0[8 * HD + 1] = o[nt][3];
+    }
+    if ((lane & 3) == 0) {
+        red_m[warp * 16 + r0] = m_run[0]; red_m[warp * 16 + r0 + 8] = m_run[1];
+        red_l[warp * 16 + r0] = l_run[0]; red_l[warp * 16 + r0 + 8] = l_run[1];
+    }
+    __syncthreads();
+    for (int i = tid; i < g * HD; i += ATT_THREADS) {
+        const int r = i / HD, d = i % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 16 + r]);
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2_guard(red_m[w * 16 + r], Mu);
+            acc += red_o[((size_t)w * 16 + r) * HD + d] * f;
+            L += red_l[w * 16 + r] * f;
+        }
+        po[(size_t)r * nsplit * HD + d] = acc;
+        if (d == 0) {
+            pml[(size_t)r * nsplit * 2] = M;
+            pml[(size_t)r * nsplit * 2 + 1] = L;
+        }
+    }
+}
+
+// merge the splits: out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  int nsplit, __nv_bfloat16* __restrict__ out, int out_stride, int nh) {
+    const int t = blockIdx.x / nh, h = blockIdx.x % nh;
+    const float* po = part_o + (size_t)blockIdx.x * nsplit * HD;
+    const float* pml = part_ml + (size_t)blockIdx.x * nsplit * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
+    for (int s = 0; s < nsplit; ++s) L += pml[2 * s + 1] * exp2_guard(pml[2 * s], Mu);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < nsplit; ++s) acc += po[(size_t)s * HD + d] * exp2_guard(pml[2 * s], Mu);
+        out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// prefill / portions
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                    int out_stride, const __nv_bfloat16* __restrict__ kc,
+                    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
+                    int bt_width, const int* __restrict__ seg_start, const int* __restrict__ cached_len,
+                    int nh, int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
+                    int* err) {
+    constexpr int STRIDE = TileRow<HD>::STRIDE;
+    constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
+    const int seg = blockIdx.z, h = blockIdx.y;
+    const int s0 = seg_start[seg], qlen = seg_start[seg + 1] - s0;
+    const int q0 = blockIdx.x * PRE_ROWS;
+    if (q0 >= qlen) return;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][STRIDE]
+    __nv_bfloat16* KV = Qs + PRE_ROWS * STRIDE;                      // [stage][K|V][64][STRIDE]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rows = min(PRE_ROWS, qlen - q0);
+    const int tok0 = s0 + q0;
+    const int pos0 = cached_len[seg] + q0;
+    const int kvh = h / (nh / nkv);
+    const int* bt = block_table + (size_t)seg * bt_width;
+    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int hi = pos0 + rows - 1;
+    const int t0 = lo / ATT_TILE, t1 = hi / ATT_TILE + 1;
+
+    for (int i = tid; i < PRE_ROWS * (HD / 8); i += ATT_THREADS) {
+        const int r = i / (HD / 8), c = i % (HD / 8);
+        const bool valid = r < rows;
+        cp_async16(Qs + r * STRIDE + c * 8, q + (size_t)(tok0 + (valid ? r : 0)) * q_stride + (size_t)h * HD + c * 8, valid);
+    }
+    auto load_tile = [&](int tile, int stage) {
+        __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
+        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
+                                                page_shift, num_pages, nkv, kvh, err);
+    };
+    load_tile(t0, 0);
+    cp_async_commit();
+
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int mat = lane >> 3, lr = lane & 7;
+    const int p_row[2] = {pos0 + warp * 16 + (lane >> 2), pos0 + warp * 16 + (lane >> 2) + 8};
+
+    for (int tile = t0; tile < t1; ++tile) {
+        const int it = tile - t0;
+        if (tile + 1 < t1) load_tile(tile + 1, (it + 1) % PRE_STAGES);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldmatrix_x4(qf[ks], Qs + (warp * 16 + lr + (mat & 1) * 8) * STRIDE + ks * 16 + (mat >> 1) * 8);
+        }
+        const __nv_bfloat16* Ks = KV + (size_t)(it % PRE_STAGES) * 2 * TILE_ELEMS;
+        const __nv_bfloat16* Vs = Ks + TILE_ELEMS;
+        // a warp whose 16 rows all sit before this tile's first key has nothing to do here
+        const bool warp_active = tile * ATT_TILE <= pos0 + warp * 16 + 15;
+        if (warp_active) {
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, Ks + (np * 16 + (mat >> 1) * 8 + lr) * STRIDE + ks * 16 + (mat & 1) * 8);
+                    mma_bf16_16816(s[2 * np], qf[ks], b[0], b[1]);
+                    mma_bf16_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+                }
+            }
+            const int key0 = tile * ATT_TILE + (lane & 3) * 2;
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + nt * 8 + (e & 1);
+                    const int p = p_row[e >> 1];
+                    const bool vis = key <= p && key >= lo && (window <= 0 || key > p - window);
+                    const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float corr[2], mu[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                mu[r] = m_new == -INFINITY ? 0.f : m_new;
+                corr[r] = exp2_guard(m_run[r], mu[r]);
+                m_run[r] = m_new;
+                l_run[r] *= corr[r];
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2_guard(s[nt][e], mu[e >> 1]);
+                    s[nt][e] = p;
+                    l_run[e >> 1] += p;
+                }
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                                  pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+                for (int j = 0; j < HD / 16; ++j) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, Vs + (kk * 16 + (mat & 1) * 8 + lr) * STRIDE + j * 16 + (mat >> 1) * 8);
+                    mma_bf16_16816(o[2 * j], pa, b[0], b[1]);
+                    mma_bf16_16816(o[2 * j + 1], pa, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    const int r0 = warp * 16 + (lane >> 2);
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+        const int d = nt * 8 + (lane & 3) * 2;
+        if (r0 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + r0) * out_stride + (size_t)h * HD + d) =
+                pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+        if (r0 + 8 < rows)
+            *reinterpret_cast<uint32_t*>(out + (size_t)(tok0 + r0 + 8) * out_stride + (size_t)h * HD + d) =
+                pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+    }
+}
+
+inline int page_shift_of(int page_size) {
+    if (page_size <= 0 || (page_size & (page_size - 1))) return -1;
+    int s = 0;
+    while ((1 << s) < page_size) ++s;
+    return s;
+}
+
+template <int HD> constexpr size_t dec_smem() {
+    return (size_t)(16 + DEC_STAGES * 2 * ATT_TILE) * TileRow<HD>::STRIDE * sizeof(__nv_bfloat16);
+}
+template <int HD> constexpr size_t pre_smem() {
+    return (size_t)(PRE_ROWS + PRE_STAGES * 2 * ATT_TILE) * TileRow<HD>::STRIDE * sizeof(__nv_bfloat16);
+}
+
+template <int HD>
+int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int out_stride,
+                  const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
+                  const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
+                  int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
+                  int* err, cudaStream_t stream) {
+    static_assert(dec_smem<HD>() >= (size_t)(4 * 16 * HD + 128) * sizeof(float) + 16 * TileRow<HD>::STRIDE * 2, "merge scratch must fit");
+    auto kern = attn_decode_kernel<HD>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
+    dim3 grid(nsplit, nkv, T);
+    kern<<<grid, ATT_THREADS, dec_smem<HD>(), stream>>>(q, q_stride, kc, vc, bt, bt_width, positions, tok_seg, nh, nkv,
+                                                        page_size, page_shift_of(page_size), num_pages, window, scale * 1.4426950408889634f,
+                                                        part_o, part_ml, nsplit, err);
+    attn_merge_kernel<HD><<<T * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, nsplit, out, out_stride, nh);
+    return (int)cudaPeekAtLastError();
+}
+
+template <int HD>
+int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int out_stride,
+                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
+                   const int* seg_start, const int* cached_len, int S, int max_q_len, int nh, int nkv,
+                   int page_size, int num_pages, int window, float scale, int* err, cudaStream_t stream) {
+    auto kern = attn_prefill_kernel<HD>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pre_smem<HD>());
+    dim3 grid((max_q_len + PRE_ROWS - 1) / PRE_ROWS, nh, S);
+    kern<<<grid, ATT_THREADS, pre_smem<HD>(), stream>>>(q, q_stride, out, out_stride, kc, vc, bt, bt_width, seg_start,
+                                                        cached_len, nh, nkv, page_size, page_shift_of(page_size),
+                                                        num_pages, window,
+                                                        scale * 1.4426950408889634f, err);
+    return (int)cudaPeekAtLastError();
+}
+
+}  // namespace prism
+
