@@ -2,6 +2,7 @@
 flushing L2 between timed launches, and prints achieved bandwidth or FLOP/s.
 
     python benchmarks/kernel_bench.py gemv  [--m 8]
+    python benchmarks/kernel_bench.py gemm_tc [--m 8]
     python benchmarks/kernel_bench.py attn_decode [--batch 8 --ctx 4096]
     python benchmarks/kernel_bench.py attn_prefill [--tokens 2048]
     python benchmarks/kernel_bench.py small [--m 8]       (norm, rope, swiglu, embed, sample)
@@ -58,6 +59,34 @@ def bench_gemv(args):
         t_lib = timeit(lambda: torch.mm(x, w.t()))
         gb = rows * K * 2 / 1e9
         print(f"gemv {name:16s} M={M:3d} N={N:6d} K={K:6d}: {t:8.1f} us  {gb / t * 1e6:7.0f} GB/s   "
+              f"(library mm: {t_lib:8.1f} us {gb / t_lib * 1e6:7.0f} GB/s)")
+
+
+def bench_gemm_tc(args):
+    M = args.m
+    shapes = [("qkv", 4608, H, ops.EPI_BF16, 1), ("qkv split4", 4608, H, ops.EPI_PARTIAL, 4),
+              ("o", H, H, ops.EPI_BF16, 1), ("o split5", H, H, ops.EPI_PARTIAL, 5), ("o split10", H, H, ops.EPI_PARTIAL, 10),
+              ("gate_up+swiglu", I, H, ops.EPI_SWIGLU, 1), ("gate_up", 2 * I, H, ops.EPI_BF16, 1),
+              ("down", H, I, ops.EPI_BF16, 1), ("down split5", H, I, ops.EPI_PARTIAL, 5),
+              ("down split10", H, I, ops.EPI_PARTIAL, 10), ("lm_head", V, H, ops.EPI_F32, 1)]
+    for name, N, K, epi, ks in shapes:
+        rows = 2 * N if epi == ops.EPI_SWIGLU else N
+        w = torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) * 0.02
+        x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+        if epi == ops.EPI_PARTIAL:
+            out = torch.empty(ks, M, N, device=DEV, dtype=torch.float32)
+        else:
+            out = torch.empty(M, N, device=DEV, dtype=torch.float32 if epi == ops.EPI_F32 else torch.bfloat16)
+        fn = lambda: ops.gemm_tc(x, w, None, out, epi, ksplit=ks)
+        if args.once:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            continue
+        t = timeit(fn)
+        t_lib = timeit(lambda: torch.mm(x, w.t()))
+        gb = rows * K * 2 / 1e9
+        print(f"gemm_tc {name:16s} M={M:3d} N={N:6d} K={K:6d}: {t:8.1f} us  {gb / t * 1e6:7.0f} GB/s   "
               f"(library mm: {t_lib:8.1f} us {gb / t_lib * 1e6:7.0f} GB/s)")
 
 
@@ -139,7 +168,7 @@ def bench_small(args):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn_decode", "attn_prefill", "small"])
+    ap.add_argument("what", choices=["gemv", "gemm_tc", "attn_decode", "attn_prefill", "small"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
@@ -147,5 +176,5 @@ if __name__ == "__main__":
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--once", action="store_true")
     a = ap.parse_args()
-    {"gemv": bench_gemv, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
+    {"gemv": bench_gemv, "gemm_tc": bench_gemm_tc, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,
      "small": bench_small}[a.what](a)

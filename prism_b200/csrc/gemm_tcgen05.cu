@@ -1,0 +1,397 @@
+// Weight-streaming bf16 matrix product on Blackwell's 5th-generation tensor
+// cores:  y[M, N] = x[M, K] @ W[N, K]^T  for a small number of tokens M
+// (decode), i.e. the F.linear calls of andre-fu/prism's decode path
+// (engine/executor.py:142,155,158,160,162).
+//
+// The roles are swapped with respect to the usual GEMM: 128 rows of W are the
+// M dimension of one tcgen05.mma and the (padded) tokens are its N dimension
+// (16..64), so every weight byte crosses the SM once: TMA
+// (cp.async.bulk.tensor, 128-byte swizzle) brings 128 x 64 tiles of W and the
+// matching 64-wide slice of x into a ring of shared-memory stages, one
+// elected thread issues tcgen05.mma (operands straight from shared memory,
+// float32 accumulator in tensor memory), tcgen05.commit releases a stage back
+// to the TMA producer, and four epilogue warps read the accumulator with
+// tcgen05.ld.  Nothing passes through registers on the way in, so the load
+// pipeline is as deep as shared memory allows (6 stages of 18 KB, two CTAs
+// per SM).
+//
+//   warp 0: TMA producer      warp 1: TMEM allocation + MMA issue
+//   warps 2-5: epilogue (each reads the 32 accumulator lanes it may access)
+//
+// Epilogues: bf16 or float32 output with optional bias; partial sums of a
+// K-split (grid.y) as float32 [split, M, N] for the next kernel to add (the
+// fused residual-add + RMSNorm takes such a stack); "paired SwiGLU": two
+// weight tiles per stage (gate rows m.., up rows I + m..), two accumulators,
+// output silu(gate) * up.
+//
+// Every mbarrier wait is bounded (about two seconds): on expiry the kernel
+// records PRISM_ERR_WAIT_TIMEOUT, all roles fall through to the common exit,
+// tensor memory is released and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace prism {
+namespace tc {
+
+constexpr int TILE_M = 128;          // weight rows per CTA tile (UMMA M)
+constexpr int TILE_K = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;         // 6 warps
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P1;\n\t}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer();
+    while (true) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);          // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: next 8-row group
+    d |= (uint64_t)1 << 46;                          // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+template <int NTOK> __device__ __forceinline__ void tmem_load(uint32_t taddr, float (&v)[NTOK]);
+template <> __device__ __forceinline__ void tmem_load<16>(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <> __device__ __forceinline__ void tmem_load<32>(uint32_t taddr, float (&v)[32]) {
+    float a[16], b[16];
+    tmem_load<16>(taddr, a);
+    tmem_load<16>(taddr + 16, b);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { v[i] = a[i]; v[16 + i] = b[i]; }
+}
+template <> __device__ __forceinline__ void tmem_load<64>(uint32_t taddr, float (&v)[64]) {
+    float a[32], b[32];
+    tmem_load<32>(taddr, a);
+    tmem_load<32>(taddr + 32, b);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { v[i] = a[i]; v[32 + i] = b[i]; }
+}
+
+template <int NTOK, int EPI> struct Cfg {
+    static constexpr int W_TILES = EPI == EPI_SWIGLU ? 2 : 1;
+    static constexpr int STAGE_BYTES = W_TILES * TILE_M * TILE_K * 2 + NTOK * TILE_K * 2;
+    static constexpr int FIT = 208 * 1024 / STAGE_BYTES;
+    static constexpr int STAGES = FIT >= 6 ? 6 : (FIT >= 2 ? FIT : 2);
+    static constexpr int TMEM_COLS = (W_TILES * NTOK) <= 32 ? 32 : ((W_TILES * NTOK) <= 64 ? 64 : 128);
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int NTOK, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 const void* __restrict__ bias, int bias_bf16, void* __restrict__ y, int ldy, int M, int N, int K,
+                 int kblocks_per_split, int pair_offset, float* __restrict__ ws, int* __restrict__ counters, int* err) {
+    using C = Cfg<NTOK, EPI>;
+    constexpr int W_TILES = C::W_TILES;
+    constexpr int STAGES = C::STAGES;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    __shared__ int abort_flag;
+    __shared__ int is_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TILE_M;                    // first weight row (output feature) of this tile
+    const int total_kb = (K + TILE_K - 1) / TILE_K;
+    const int kb0 = blockIdx.y * kblocks_per_split;
+    const int kb1 = min(total_kb, kb0 + kblocks_per_split);
+    const int nkb = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(C::TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    volatile int* abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ---- TMA producer ---------------------------------------------------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abortp)) break;
+                unsigned char* st = tiles + (size_t)s * C::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+                const int kc = (kb0 + i) * TILE_K;
+#pragma unroll
+                for (int w = 0; w < W_TILES; ++w)
+                    tma_load_2d(st + w * TILE_M * TILE_K * 2, &map_w, &full_bar[s], kc, m0 + w * pair_offset);
+                tma_load_2d(st + W_TILES * TILE_M * TILE_K * 2, &map_x, &full_bar[s], kc, 0);
+                issued = i + 1;
+            }
+            if (*abortp) {
+                // give the copies already in flight a bounded chance to land before the CTA's memory is reused
+                for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1, abortp);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) |
+                                       ((uint32_t)(TILE_M >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abortp);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = smem_addr(tiles + (size_t)s * C::STAGE_BYTES);
+                const uint64_t db = umma_desc(st + W_TILES * TILE_M * TILE_K * 2);
+#pragma unroll
+                for (int w = 0; w < W_TILES; ++w) {
+                    const uint64_t da = umma_desc(st + w * TILE_M * TILE_K * 2);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        umma_bf16(tmem_base + w * NTOK, da + (uint64_t)(k * UMMA_K * 2 >> 4), db + (uint64_t)(k * UMMA_K * 2 >> 4),
+                                  idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
+            }
+            umma_commit(acc_bar);                    // the accumulator is complete (or as far as it got)
+        }
+    } else {
+        // ---- epilogue: warps 2..5, TMEM lanes (warp % 4) * 32 .. + 31 -----------------
+        const int q = warp & 3;
+        const int m = m0 + q * 32 + lane;            // this thread's output feature
+        if (nkb > 0) mbar_wait(acc_bar, 0, abortp);      // on expiry this sets the abort flag
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps agree on the flag
+        const bool go = *abortp == 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (go) {
+            float acc[W_TILES][NTOK];
+            if (nkb > 0) {
+#pragma unroll
+                for (int w = 0; w < W_TILES; ++w)
+                    tmem_load<NTOK>(tmem_base + ((uint32_t)(q * 32) << 16) + w * NTOK, acc[w]);
+            } else {
+#pragma unroll
+                for (int w = 0; w < W_TILES; ++w)
+#pragma unroll
+                    for (int n = 0; n < NTOK; ++n) acc[w][n] = 0.f;
+            }
+            bool finish = true;
+            if ((EPI == EPI_BF16 || EPI == EPI_F32) && gridDim.y > 1) {
+                // K was split over gridDim.y CTAs: every CTA leaves its partial sums in the workspace and
+                // the one that arrives last at the tile's counter adds them up, in split order, and
+                // finishes the tile.  Nobody waits for anybody.
+                if (m < N)
+#pragma unroll
+                    for (int n = 0; n < NTOK; ++n)
+                        if (n < M) ws[((size_t)blockIdx.y * M + n) * N + m] = acc[0][n];
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
+                if (threadIdx.x == 64) {
+                    const int old = atomicAdd(&counters[blockIdx.x], 1);
+                    is_last = old == (int)gridDim.y - 1;
+                    if (is_last) counters[blockIdx.x] = 0;                 // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                finish = is_last != 0;
+                if (finish && m < N) {
+                    __threadfence();
+#pragma unroll
+                    for (int n = 0; n < NTOK; ++n) {
+                        if (n >= M) continue;
+                        float v = 0.f;
+                        for (int sp = 0; sp < (int)gridDim.y; ++sp) v += __ldcg(&ws[((size_t)sp * M + n) * N + m]);
+                        acc[0][n] = v;
+                    }
+                }
+            }
+            if (finish && m < N) {
+                const float b = (EPI == EPI_BF16 || EPI == EPI_F32) && bias != nullptr ? load_param(bias, bias_bf16, m) : 0.f;
+#pragma unroll
+                for (int n = 0; n < NTOK; ++n) {
+                    if (n >= M) continue;
+                    if (EPI == EPI_SWIGLU) {
+                        const float g = acc[0][n], u = acc[W_TILES - 1][n];
+                        reinterpret_cast<__nv_bfloat16*>(y)[(size_t)n * ldy + m] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                    } else if (EPI == EPI_PARTIAL) {
+                        reinterpret_cast<float*>(y)[((size_t)blockIdx.y * M + n) * ldy + m] = acc[0][n];
+                    } else if (EPI == EPI_F32) {
+                        reinterpret_cast<float*>(y)[(size_t)n * ldy + m] = acc[0][n] + b;
+                    } else {
+                        reinterpret_cast<__nv_bfloat16*>(y)[(size_t)n * ldy + m] = __float2bfloat16_rn(acc[0][n] + b);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag) report_error(err, PRISM_ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS));
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A [rows, cols] row-major bf16 matrix with row pitch ld (elements); box = 64 columns x box_rows rows.
+inline int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int NTOK, int EPI>
+int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, const void* bias, int bias_bf16, void* y,
+           int ldy, int M, int N, int K, int ksplit, int pair_offset, float* ws, int* counters, int* err,
+           cudaStream_t stream) {
+    using C = Cfg<NTOK, EPI>;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, w_rows, K, ldw, TILE_M);
+    if (rc) return rc;
+    rc = make_map(&mx, x, M, K, ldx, NTOK);
+    if (rc) return rc;
+    const int total_kb = (K + TILE_K - 1) / TILE_K;
+    const int per = (total_kb + ksplit - 1) / ksplit;
+    auto kern = gemm_swap_kernel<NTOK, EPI>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    dim3 grid((N + TILE_M - 1) / TILE_M, ksplit);
+    kern<<<grid, THREADS, C::SMEM, stream>>>(mw, mx, bias, bias_bf16, y, ldy, M, N, K, per, pair_offset, ws, counters, err);
+    return (int)cudaPeekAtLastError();
+}
+
+}  // namespace tc
+}  // namespace prism
+
+// 1 if the kernel takes these sizes: up to 64 tokens, K a multiple of 8 (16-byte rows for TMA).
+PRISM_EXPORT int prism_gemm_tcgen05_supported(int M, int N, int K) {
+    return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0;
+}
+
+// epi: 0 bf16 (+bias), 1 float32 (+bias), 2 paired SwiGLU (W is [2N, K]; bf16 out [M, N]),
+// 3 partial sums: y is float32 [ksplit, M, N] (ldy = N), no bias.
+// ksplit > 1 with epi 0 or 1 needs a workspace `ws` of ksplit * M * N floats and `counters`, one int per
+// 128-row tile of N, zero before the first launch (the kernel leaves them zero); the last CTA of each
+// tile adds the partial sums in split order, so the result does not depend on timing.  Not with epi 2.
+PRISM_EXPORT int prism_gemm_tcgen05(const void* W, int ldw, const void* x, int ldx, const void* bias, int bias_dtype,
+                                    void* y, int ldy, int M, int N, int K, int epi, int ksplit, float* ws,
+                                    int* counters, int* err, cudaStream_t stream) {
+    using namespace prism::tc;
+    if (M <= 0 || N <= 0) return 0;
+    if (!prism_gemm_tcgen05_supported(M, N, K) || ldw % 8 || ldx % 8 || ksplit < 1 || (ksplit > 1 && epi == EPI_SWIGLU) ||
+        (ksplit > 1 && epi != EPI_PARTIAL && (ws == nullptr || counters == nullptr)) ||
+        ((uintptr_t)W & 15) || ((uintptr_t)x & 15))
+        return (int)cudaErrorInvalidValue;
+    const int bb = bias_dtype == PRISM_DTYPE_BF16;
+    const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const long long w_rows = epi == EPI_SWIGLU ? 2LL * N : N;
+    const int pair = epi == EPI_SWIGLU ? N : 0;
+#define ARGS W, ldw, w_rows, x, ldx, bias, bb, y, ldy, M, N, K, ksplit, pair, ws, counters, err, stream
+#define BY_N(E) (ntok == 16 ? launch<16, E>(ARGS) : ntok == 32 ? launch<32, E>(ARGS) : launch<64, E>(ARGS))
+    switch (epi) {
+        case EPI_BF16: return BY_N(EPI_BF16);
+        case EPI_F32: return BY_N(EPI_F32);
+        case EPI_SWIGLU: return BY_N(EPI_SWIGLU);
+        case EPI_PARTIAL: return BY_N(EPI_PARTIAL);
+    }
+#undef BY_N
+#undef ARGS
+    return (int)cudaErrorInvalidValue;
+}

@@ -202,6 +202,8 @@ class ModelRunner:
     # ---- errors ---------------------------------------------------------------------
     def check_errors(self) -> None:
         """Read the device error word (synchronises) and raise if a kernel set it."""
+        from .. import ops
+        ops.check_tc_errors()
         code = int(self.err.item())
         if code:
             self.err.zero_()

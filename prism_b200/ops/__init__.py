@@ -92,6 +92,8 @@ class _Sig:
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
+    prism_gemm_tcgen05_supported = [_i, _i, _i]
+    prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]
     prism_gemv_bf16_supported = [_i, _i, _i]
     prism_gemv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]
 
@@ -197,6 +199,104 @@ def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
                                  M, N, K, epi, _stream()), "gemv_bf16")
 
 
+EPI_PARTIAL = 3
+_tc_err = {}
+
+
+def _tc_err_word(device) -> torch.Tensor:
+    """Device error word for the tensor-core GEMM's bounded waits (one per device)."""
+    key = torch.device(device).index or 0
+    if key not in _tc_err:
+        _tc_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_err[key]
+
+
+_tc_ws = {}
+
+
+def _tc_workspace(device, floats: int, tiles: int):
+    """Split-K workspace of the tensor-core GEMM: partial sums and one counter per
+    tile.  Grown outside graph capture only; kernels leave the counters at zero."""
+    key = torch.device(device).index or 0
+    ws = _tc_ws.get(key)
+    if ws is None or ws[0].numel() < floats or ws[1].numel() < tiles:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the split-K workspace must be sized before graph capture (run one step eagerly first)")
+        ws = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
+              torch.zeros(max(tiles, 4096), dtype=torch.int32, device=device))
+        _tc_ws[key] = ws
+    return ws
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+            epi: int = EPI_BF16, ksplit: int = 1, err: Optional[torch.Tensor] = None):
+    """tcgen05 + TMA weight-streaming product for up to 64 tokens.  ``epi``:
+    ``EPI_BF16`` / ``EPI_F32`` (``out [M, N]``, + bias), ``EPI_SWIGLU`` (``w`` is
+    the fused ``[2N, K]`` gate/up weight), ``EPI_PARTIAL`` (``out`` float32
+    ``[ksplit, M, N]`` partial sums over K for the next kernel to add)."""
+    _cuda(x, w, bias, out)
+    M, K = x.shape
+    N = out.shape[-1]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.is_contiguous()
+    assert w.shape[0] == (2 * N if epi == EPI_SWIGLU else N)
+    if epi == EPI_PARTIAL:
+        assert out.dtype == torch.float32 and out.shape == (ksplit, M, N) and bias is None
+    else:
+        assert out.shape == (M, N) and (ksplit == 1 or epi != EPI_SWIGLU)
+        assert out.dtype == (torch.float32 if epi == EPI_F32 else torch.bfloat16)
+    err = err if err is not None else _tc_err_word(x.device)
+    ws = cnt = None
+    if ksplit > 1 and epi != EPI_PARTIAL:
+        ws, cnt = _tc_workspace(x.device, ksplit * M * N, (N + 127) // 128)
+    _check(lib().prism_gemm_tcgen05(_ptr(w), w.stride(0), _ptr(x), x.stride(0) if M > 1 else K, _ptr(bias),
+                                    F32 if bias is None else _dt(bias), _ptr(out), N, M, N, K, epi, ksplit,
+                                    _ptr(ws), _ptr(cnt), _ptr(err), _stream()), "gemm_tcgen05")
+
+
+USE_TC_GEMM = os.environ.get("PRISM_TC_GEMM", "1") != "0"
+TC_GEMM_MAX_M = int(os.environ.get("PRISM_TC_GEMM_MAX_M", "16"))
+
+
+def tc_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 weight-streaming product takes this call."""
+    M, K = x.shape
+    return (USE_TC_GEMM and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= TC_GEMM_MAX_M
+            and x.stride(1) == 1 and w.stride(1) == 1 and (M == 1 or x.stride(0) % 8 == 0) and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(lib().prism_gemm_tcgen05_supported(M, w.shape[0], K)))
+
+
+def tc_ksplit(N: int, K: int) -> int:
+    """CTAs that share one 128-row tile's K range: about one CTA per SM in all,
+    at least 8 blocks of 64 k each."""
+    tiles = (N + 127) // 128
+    return max(1, min(NUM_SMS // tiles, ((K + 63) // 64) // 8))
+
+
+def check_tc_errors():
+    """Raise if a bounded wait of the tensor-core GEMM ran out (synchronises)."""
+    for word in _tc_err.values():
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise KernelError(f"tensor-core GEMM: device error {code} (a bounded wait ran out)")
+
+
+def linear_delta(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A projection whose result will be added to the residual stream by the
+    next norm: like ``linear``, but it may return a float32 stack ``[k, M, N]``
+    of partial sums over K, which the fused add + norm kernel adds up."""
+    if bias is None and tc_gemm_ok(x, w):
+        N, K = w.shape
+        ks = tc_ksplit(N, K)
+        if ks > 1:
+            out = torch.empty((ks, x.shape[0], N), dtype=torch.float32, device=x.device)
+            gemm_tc(x, w, None, out, EPI_PARTIAL, ksplit=ks)
+            return out
+    return linear(x, w, bias)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x @ w.T + bias`` with ``w`` in the ``[out, in]`` layout of the model
@@ -219,6 +319,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             out.copy_(o32)
             return out
         return o32.to(want)
+    if want in (torch.float32, torch.bfloat16) and tc_gemm_ok(x, w) and (out is None or out.is_contiguous()):
+        if out is None or out.dtype != want:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        gemm_tc(x, w, bias, out, EPI_F32 if want == torch.float32 else EPI_BF16, ksplit=tc_ksplit(N, x.shape[1]))
+        return out
     if USE_GEMV_PLAIN and want in (torch.float32, torch.bfloat16) and M <= GEMV_MAX_M and x.stride(-1) == 1 \
             and (out is None or out.stride(-1) == 1) and gemv_supported(M, N, x.shape[1]) \
             and (M == 1 or x.stride(0) % 8 == 0):
@@ -408,12 +513,16 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
 def feed_forward_swiglu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor):
     """``down(silu(gate(x)) * up(x))`` with the fused gate/up weight."""
     M, I = x.shape[0], gate_up_w.shape[0] // 2
+    if tc_gemm_ok(x, gate_up_w):
+        act = ctx.alloc((M, I), x.dtype)
+        gemm_tc(x, gate_up_w, None, act, EPI_SWIGLU)       # gate/up product with the SwiGLU in its epilogue
+        return linear_delta(act, down_w)
     if x.dtype == torch.bfloat16 and gate_up_w.dtype == torch.bfloat16 and M <= GEMV_MAX_M \
             and gemv_supported(M, I, x.shape[1]) and (M == 1 or x.stride(0) % 8 == 0):
         act = ctx.alloc((M, I), x.dtype)
         gemv(x, gate_up_w, None, act, EPI_SWIGLU)        # gate/up product with the SwiGLU in its epilogue
-        return linear(act, down_w)
+        return linear_delta(act, down_w)
     gu = linear(x, gate_up_w)
     act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
     swiglu(gu, act)
-    return linear(act, down_w)
+    return linear_delta(act, down_w)

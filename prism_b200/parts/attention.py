@@ -73,4 +73,4 @@ class GQAAttention(Mixer):
                           cache.block_table, cache.num_pages, ctx.max_positions, ctx.err, table=table)
         attn = ctx.alloc((T, qs), x.dtype)
         ops.attention(ctx, q, attn, cache, self.window, self.scale)
-        return ops.linear(attn, self.w["o_w"], self.w.get("o_b"))
+        return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))

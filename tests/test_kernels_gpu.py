@@ -210,6 +210,48 @@ def test_gemv_bf16(M, N, K):
         assert torch.allclose(act.float(), r, atol=1e-2 * float(r.abs().max()) + 1e-3, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(256, 128), (4608, 3584), (3584, 18944), (100, 96), (1000, 40), (130, 3000), (9507, 512)])
+def test_gemm_tcgen05(M, N, K):
+    """The tcgen05 + TMA weight-streaming product alone: every epilogue, K tails
+    (K % 64 != 0), N tails (N % 128 != 0), token counts up to 64, K-splits."""
+    ops = _ops()
+    x = _rand((M, K), torch.bfloat16, 40)
+    w = _rand((N, K), torch.bfloat16, 41, 0.05)
+    b = _rand((N,), torch.bfloat16, 42)
+    err = _err()
+    ref = x.float() @ w.float().T
+    scale = float(ref.abs().max())
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, w, b, out, ops.EPI_BF16, err=err)
+    assert int(err) == 0
+    assert torch.allclose(out.float(), ref + b.float(), atol=8e-3 * scale + 8e-3, rtol=1e-2)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, w, None, out32, ops.EPI_F32, err=err)
+    assert torch.allclose(out32, ref, atol=2e-3 * scale, rtol=2e-3)
+    for ks in (2, 5):
+        part = torch.full((ks, M, N), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_tc(x, w, None, part, ops.EPI_PARTIAL, ksplit=ks, err=err)
+        assert torch.allclose(part.sum(0), ref, atol=2e-3 * scale, rtol=2e-3)
+        # split K with the sum inside the kernel (the last CTA of a tile adds up): twice, same bits
+        o1 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        o2 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        o3 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_tc(x, w, b, o1, ops.EPI_BF16, ksplit=ks, err=err)
+        ops.gemm_tc(x, w, b, o2, ops.EPI_F32, ksplit=ks, err=err)
+        ops.gemm_tc(x, w, b, o3, ops.EPI_F32, ksplit=ks, err=err)
+        assert torch.allclose(o1.float(), ref + b.float(), atol=8e-3 * scale + 8e-3, rtol=1e-2)
+        assert torch.allclose(o2, ref + b.float(), atol=2e-3 * scale, rtol=2e-3) and torch.equal(o2, o3)
+    if N % 2 == 0:
+        I = N // 2
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tc(x, w, None, act, ops.EPI_SWIGLU, err=err)
+        g, u = ref[:, :I], ref[:, I:]
+        r = g * torch.sigmoid(g) * u
+        assert torch.allclose(act.float(), r, atol=1e-2 * float(r.abs().max()) + 1e-3, rtol=2e-2)
+    assert int(err) == 0
+
+
 @pytest.mark.parametrize("T,I", [(3, 100), (40, 18944)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu(T, I, dtype):
