@@ -153,6 +153,12 @@ def run(args):
         runner.check_errors()
         return ms, launches, ctx_mean, ck
 
+    if args.quick:
+        # decode only, for profilers: no prefill timing, no other batch sizes, no end-to-end run
+        ms, launches, ctx_mean, _ = decode_bench(B, K, Wm)
+        print(json.dumps({"quick": True, "batch": B, "layers": cfg["num_hidden_layers"], "ms_per_step": round(ms, 4),
+                          "tok_s": round(B / ms * 1e3, 1), "gpu_launches": int(launches)}))
+        return
     # ---- prefill of one 2,048-token prompt -------------------------------------
     runner.begin_request("pf")
     p = prompts(1)[0]
@@ -230,6 +236,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--quick", action="store_true", help="decode at --batch only (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

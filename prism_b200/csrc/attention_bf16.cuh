@@ -4,7 +4,8 @@
 //    split of the keys); the nh/nkv query heads of that kv head form the rows
 //    of one 16-row MMA tile, so a K/V tile is read once for all of them.  Four
 //    warps each take 16 of a tile's 64 keys; partial (max, sum, output) of the
-//    warps and then of the splits are merged by a second small kernel.
+//    warps are merged in shared memory, those of the splits by the CTA that
+//    finishes last (or, without a counter array, by a second small kernel).
 //  * prefill / portions: a CTA takes 64 query rows of one head of one
 //    segment; keys come from the request's pages (earlier portions and this
 //    one), causal with the portion's offset: the row at position p sees keys
@@ -42,7 +43,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const int* __restrict__ block_table, int bt_width,
                    const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh,
                    int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit, int* err) {
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit,
+                   __nv_bfloat16* __restrict__ out, int out_stride, int* __restrict__ counters, int* err) {
+    pdl_wait();
+    __shared__ int s_last;
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -63,12 +67,47 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
     float* po = part_o + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * HD;   // + row * nsplit * HD
     float* pml = part_ml + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * 2;
+    // With `counters` the splits are merged here: every CTA leaves its partial result, and the CTA that
+    // arrives last at the (token, kv head) counter adds them up in split order and writes the output
+    // rows.  Nobody waits.  Without `counters` a second kernel merges.
+    auto merge_if_last = [&]() {
+        if (counters == nullptr) return;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int* c = counters + (size_t)t * nkv + kvh;
+            const int old = atomicAdd(c, 1);
+            s_last = old == nsplit - 1;
+            if (s_last) *c = 0;                       // ready for the next launch
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        const float* bo = part_o + ((size_t)t * nh + (size_t)kvh * g) * nsplit * HD;
+        const float* bml = part_ml + ((size_t)t * nh + (size_t)kvh * g) * nsplit * 2;
+        for (int i = tid; i < g * HD; i += ATT_THREADS) {
+            const int r = i / HD, d = i % HD;
+            const float* ml = bml + (size_t)r * nsplit * 2;
+            float M = -INFINITY;
+            for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(ml + 2 * sp));
+            const float Mu = M == -INFINITY ? 0.f : M;
+            float L = 0.f, acc = 0.f;
+            for (int sp = 0; sp < nsplit; ++sp) {
+                const float f = exp2_guard(__ldcg(ml + 2 * sp), Mu);
+                L += __ldcg(ml + 2 * sp + 1) * f;
+                acc += __ldcg(bo + ((size_t)r * nsplit + sp) * HD + d) * f;
+            }
+            out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+    };
     if (t0 >= t1) {           // nothing for this split: an empty partial
         for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * nsplit * HD + i % HD] = 0.f;
         for (int r = tid; r < g; r += ATT_THREADS) {
             pml[(size_t)r * nsplit * 2] = -INFINITY;
             pml[(size_t)r * nsplit * 2 + 1] = 0.f;
         }
+        pdl_trigger_gemm();
+        merge_if_last();
         return;
     }
 
@@ -161,6 +200,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         __syncthreads();
     }
     cp_async_wait<0>();
+    pdl_trigger_gemm();     // the keys are read: the next kernel may start its prologue
 
     // merge the four warps' partials through shared memory
 #pragma unroll
@@ -203,12 +243,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             pml[(size_t)r * nsplit * 2 + 1] = L;
         }
     }
+    merge_if_last();
 }
 
 // merge the splits: out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   int nsplit, __nv_bfloat16* __restrict__ out, int out_stride, int nh) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
     const float* po = part_o + (size_t)blockIdx.x * nsplit * HD;
     const float* pml = part_ml + (size_t)blockIdx.x * nsplit * 2;
@@ -236,6 +279,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                     int bt_width, const int* __restrict__ seg_start, const int* __restrict__ cached_len,
                     int nh, int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                     int* err) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
     const int seg = blockIdx.z, h = blockIdx.y;
@@ -397,16 +442,17 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
                   const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
                   int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
-                  int* err, cudaStream_t stream) {
+                  int* err, cudaStream_t stream, int* counters = nullptr) {
     static_assert(dec_smem<HD>() >= (size_t)(4 * 16 * HD + 128) * sizeof(float) + 16 * TileRow<HD>::STRIDE * 2, "merge scratch must fit");
     auto kern = attn_decode_kernel<HD>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
     dim3 grid(nsplit, nkv, T);
-    kern<<<grid, ATT_THREADS, dec_smem<HD>(), stream>>>(q, q_stride, kc, vc, bt, bt_width, positions, tok_seg, nh, nkv,
-                                                        page_size, page_shift_of(page_size), num_pages, window, scale * 1.4426950408889634f,
-                                                        part_o, part_ml, nsplit, err);
-    attn_merge_kernel<HD><<<T * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, nsplit, out, out_stride, nh);
-    return (int)cudaPeekAtLastError();
+    cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
+                                   positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
+                                   scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, counters, err);
+    if (rc != cudaSuccess || counters != nullptr) return (int)rc;
+    return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD >= 128 ? 128 : 64), 0, stream,
+                              (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);
 }
 
 template <int HD>

@@ -53,6 +53,8 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
                                     const int* __restrict__ tok_seg, int Ttot, int nh, int nkv,
                                     int hd, int page_size, int num_pages, int window, float scale,
                                     int* err) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + warp;

@@ -29,7 +29,8 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
-LINK_LIBS = ["-lcuda"]
+NVCC_FLAGS += os.environ.get("PRISM_NVCC_EXTRA", "").split()      # experiments: extra -D flags
+LINK_LIBS = []
 
 
 class BuildError(RuntimeError):

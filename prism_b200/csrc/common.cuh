@@ -30,6 +30,54 @@
 
 namespace prism {
 
+// Programmatic dependent launch.  A kernel launched with the attribute below may
+// start while the kernel before it in the stream is still running; it must call
+// pdl_wait() before it reads or writes anything that kernel (or an earlier one)
+// touches - the call returns once all of the earlier grid's memory operations
+// are done and visible.  pdl_trigger() tells the runtime that the next kernel
+// may be launched as soon as every CTA of this one has started.  Both are
+// no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#ifndef PRISM_PDL_TRIGGER_SMALL
+#define PRISM_PDL_TRIGGER_SMALL 1
+#endif
+#ifndef PRISM_PDL_TRIGGER_GEMM
+#define PRISM_PDL_TRIGGER_GEMM 1
+#endif
+__device__ __forceinline__ void pdl_trigger() {
+#if PRISM_PDL_TRIGGER_SMALL
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_trigger_gemm() {
+#if PRISM_PDL_TRIGGER_GEMM
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+// 1: kernels of this library are launched with programmatic stream serialization
+// (the default); 0: plain launches.  Set through prism_set_pdl().
+inline int& pdl_enabled() {
+    static int on = 1;
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ void report_error(int* err, int code) {
     if (err != nullptr) atomicCAS(err, 0, code);
 }

@@ -9,6 +9,8 @@ namespace prism {
 template <typename W>
 __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ table,
                              float* __restrict__ out, int H, int V, int* err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -36,8 +38,8 @@ PRISM_EXPORT int prism_embed(const int* ids, const void* table, int table_dtype,
     if (T <= 0) return 0;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (table_dtype == PRISM_DTYPE_BF16)
-        prism::embed_kernel<<<T, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V, err);
-    else
-        prism::embed_kernel<<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V, err);
-    return (int)cudaPeekAtLastError();
+        return (int)prism::launch_kernel(prism::embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, ids,
+                                         (const __nv_bfloat16*)table, out, H, V, err);
+    return (int)prism::launch_kernel(prism::embed_kernel<float>, dim3(T), dim3(threads), 0, stream, ids,
+                                     (const float*)table, out, H, V, err);
 }

@@ -14,6 +14,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 sgemm_nt_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
                 const void* __restrict__ bias, int bias_bf16, float* __restrict__ C, int ldc,
                 int M, int N, int K) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int THREADS = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];

@@ -185,11 +185,27 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
     if (warp == 0) {
         // ---- TMA producer ---------------------------------------------------------
+        // W does not depend on the kernels before this one: its first STAGES tiles are requested
+        // at once; the activations x are requested after pdl_wait(), i.e. once they exist.
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < nkb; ++i) {
+            const int pre = min(nkb, STAGES);
+            for (int i = 0; i < pre; ++i) {
+                unsigned char* st = tiles + (size_t)i * C::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+                const int kc = (kb0 + i) * TILE_K;
+#pragma unroll
+                for (int w = 0; w < W_TILES; ++w)
+                    tma_load_2d(st + w * TILE_M * TILE_K * 2, &map_w, &full_bar[i], kc, m0 + w * pair_offset);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + W_TILES * TILE_M * TILE_K * 2, &map_x, &full_bar[i],
+                            (kb0 + i) * TILE_K, 0);
+            issued = pre;
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abortp)) break;
+                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abortp)) break;
                 unsigned char* st = tiles + (size_t)s * C::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
                 const int kc = (kb0 + i) * TILE_K;
@@ -199,6 +215,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 tma_load_2d(st + W_TILES * TILE_M * TILE_K * 2, &map_x, &full_bar[s], kc, 0);
                 issued = i + 1;
             }
+            pdl_trigger_gemm();     // all of this CTA's loads are on their way: the next kernel may start its prologue
             if (*abortp) {
                 // give the copies already in flight a bounded chance to land before the CTA's memory is reused
                 for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1, abortp);
@@ -233,6 +250,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         // ---- epilogue: warps 2..5, TMEM lanes (warp % 4) * 32 .. + 31 -----------------
         const int q = warp & 3;
         const int m = m0 + q * 32 + lane;            // this thread's output feature
+        pdl_wait();                                      // outputs, bias, workspace: ordered after earlier kernels
         if (nkb > 0) mbar_wait(acc_bar, 0, abortp);      // on expiry this sets the abort flag
         asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps agree on the flag
         const bool go = *abortp == 0;
@@ -353,12 +371,18 @@ int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, con
     auto kern = gemm_swap_kernel<NTOK, EPI>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
     dim3 grid((N + TILE_M - 1) / TILE_M, ksplit);
-    kern<<<grid, THREADS, C::SMEM, stream>>>(mw, mx, bias, bias_bf16, y, ldy, M, N, K, per, pair_offset, ws, counters, err);
-    return (int)cudaPeekAtLastError();
+    return (int)launch_kernel(kern, grid, dim3(THREADS), C::SMEM, stream, mw, mx, bias, bias_bf16, y, ldy, M, N, K, per,
+                              pair_offset, ws, counters, err);
 }
 
 }  // namespace tc
 }  // namespace prism
+
+// Programmatic dependent launch for every kernel of this library: 1 on (default), 0 off.
+PRISM_EXPORT int prism_set_pdl(int on) {
+    prism::pdl_enabled() = on ? 1 : 0;
+    return prism::pdl_enabled();
+}
 
 // 1 if the kernel takes these sizes: up to 64 tokens, K a multiple of 8 (16-byte rows for TMA).
 PRISM_EXPORT int prism_gemm_tcgen05_supported(int M, int N, int K) {

@@ -42,6 +42,8 @@ __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_kernel(const __nv_bfloat16* __restrict__ W, int ldw, const __nv_bfloat16* __restrict__ x, int ldx,
             const void* __restrict__ bias, int bias_bf16, void* __restrict__ y, int ldy, int M, int N,
             int K, int WK, int pair_offset) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int STREAMS = EPI == EPI_SWIGLU ? 2 : 1;    // weight rows streamed per output row
     extern __shared__ float red[];                         // [8 warps][STREAMS][16][NT * 8] when WK > 1
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -20,6 +20,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    int nsplit, size_t split_stride,
                                    const void* __restrict__ weight, int weight_bf16, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int H) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -49,6 +51,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
                                        int nsplit, size_t split_stride,
                                        const void* __restrict__ weight, int weight_bf16, float eps,
                                        TO* __restrict__ out, const int* __restrict__ rows, int H) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -103,13 +107,14 @@ PRISM_EXPORT int prism_add_rmsnorm(float* residual, const void* delta, int delta
     const int iters = chunks > 1024 ? 2 : 1;
     const int threads = vec ? ((chunks + iters - 1) / iters + 31) / 32 * 32
                             : (H >= 2048 ? 256 : (H >= 512 ? 128 : 64));
+    cudaError_t rc = cudaSuccess;
 #define ARGS residual, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)out, rows, H
 #define LAUNCH(TDx, TOx)                                                                          \
     do {                                                                                          \
         using TD = TDx; using TO = TOx;                                                           \
-        if (vec && iters == 1) prism::add_rmsnorm_vec_kernel<TD, TO, 1><<<nrows, threads, 0, stream>>>(ARGS); \
-        else if (vec) prism::add_rmsnorm_vec_kernel<TD, TO, 2><<<nrows, threads, 0, stream>>>(ARGS);          \
-        else prism::add_rmsnorm_kernel<TD, TO><<<nrows, threads, 0, stream>>>(ARGS);              \
+        if (vec && iters == 1) rc = prism::launch_kernel(prism::add_rmsnorm_vec_kernel<TD, TO, 1>, dim3(nrows), dim3(threads), 0, stream, ARGS); \
+        else if (vec) rc = prism::launch_kernel(prism::add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(nrows), dim3(threads), 0, stream, ARGS);          \
+        else rc = prism::launch_kernel(prism::add_rmsnorm_kernel<TD, TO>, dim3(nrows), dim3(threads), 0, stream, ARGS);              \
     } while (0)
     if (delta_dtype == PRISM_DTYPE_BF16) {
         if (out_dtype == PRISM_DTYPE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -120,5 +125,5 @@ PRISM_EXPORT int prism_add_rmsnorm(float* residual, const void* delta, int delta
     }
 #undef LAUNCH
 #undef ARGS
-    return (int)cudaPeekAtLastError();
+    return (int)rc;
 }

@@ -22,6 +22,8 @@ __global__ void rope_kv_kernel(T* __restrict__ q, T* __restrict__ k, const T* __
                                int rd, T* __restrict__ kc, T* __restrict__ vc,
                                const int* __restrict__ block_table, int bt_width, int page_size,
                                int num_pages, int nh, int nkv, int hd, int max_pos, int* err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
@@ -84,6 +86,8 @@ __global__ void rope_kv_kernel(T* __restrict__ q, T* __restrict__ k, const T* __
 // layers and heads: table[t, j] = (cos, sin)(position[t] * inv_freq[j]), float32.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   int half, int T, float2* __restrict__ table) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= T * half) return;
     float s, c;
@@ -101,6 +105,8 @@ __global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T
                                    int rd, T* __restrict__ kc, T* __restrict__ vc,
                                    const int* __restrict__ block_table, int bt_width, int page_size,
                                    int num_pages, int nh, int nkv, int hd, int max_pos, int* err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
@@ -163,6 +169,89 @@ __global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T
     }
 }
 
+// The same rotation and store, reading q/k/v as a stack of float32 partial sums
+// [ks, T, D] of the qkv projection (D = (nh + 2 nkv) * hd; a K-split product leaves
+// them so) plus an optional bias, and writing the rotated q to its own buffer.
+// Sum, bias and rotation in float32, one rounding at each store.
+template <typename T>
+__global__ void rope_kv_partial_kernel(const float* __restrict__ parts, int ks, size_t part_stride, int D,
+                                       const void* __restrict__ bias, int bias_bf16, T* __restrict__ q_out,
+                                       int q_out_stride, const int* __restrict__ positions,
+                                       const int* __restrict__ tok_seg, const float2* __restrict__ table, int rd,
+                                       T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ block_table,
+                                       int bt_width, int page_size, int num_pages, int nh, int nkv, int hd,
+                                       int max_pos, int* err) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0) report_error(err, PRISM_ERR_POSITION_RANGE);
+        return;
+    }
+    size_t slot = 0;
+    bool store = kc != nullptr;
+    if (store) {
+        const int page = block_table[(size_t)tok_seg[t] * bt_width + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
+            store = false;
+        } else {
+            slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
+        }
+    }
+    auto load_sum8 = [&](int col, float (&v)[8]) {
+        if (bias != nullptr) load_param8(bias, bias_bf16, col, v);
+        else
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.f;
+        for (int s = 0; s < ks; ++s) {
+            float p[8];
+            load8(parts + (size_t)s * part_stride + (size_t)t * D + col, p);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += p[e];
+        }
+    };
+    const int half = rd / 2;
+    const int rot_chunks = half / 8, pass_chunks = (hd - rd) / 8, per = rot_chunks + pass_chunks;
+    const int n_q = nh * per, n_k = nkv * per, n_v = nkv * (hd / 8);
+    const float2* tab = table + (size_t)t * half;
+    for (int i = threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x) {
+        if (i < n_q + n_k) {
+            const bool is_q = i < n_q;
+            if (!is_q && !store) continue;
+            const int ii = is_q ? i : i - n_q;
+            const int h = ii / per, c = ii % per;
+            const int col0 = (is_q ? 0 : nh * hd) + h * hd;
+            T* dst = is_q ? q_out + (size_t)t * q_out_stride + h * hd : kc + slot + h * hd;
+            if (c < rot_chunks) {
+                const int j = c * 8;
+                float x1[8], x2[8], y1[8], y2[8];
+                load_sum8(col0 + j, x1);
+                load_sum8(col0 + j + half, x2);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float2 cs = tab[j + e];
+                    y1[e] = x1[e] * cs.x - x2[e] * cs.y;
+                    y2[e] = x2[e] * cs.x + x1[e] * cs.y;
+                }
+                store8(dst + j, y1);
+                store8(dst + j + half, y2);
+            } else {
+                const int d = rd + (c - rot_chunks) * 8;
+                float x[8];
+                load_sum8(col0 + d, x);
+                store8(dst + d, x);
+            }
+        } else if (store) {
+            const int d = (i - n_q - n_k) * 8;
+            float x[8];
+            load_sum8((nh + nkv) * hd + d, x);
+            store8(vc + slot + d, x);
+        }
+    }
+}
+
 }  // namespace prism
 
 // inv_freq may be null with rotary_dim 0: no rotation, only the cache store.
@@ -171,8 +260,35 @@ PRISM_EXPORT int prism_rope_table(const int* positions, const float* inv_freq, i
                                   float* table, cudaStream_t stream) {
     if (T <= 0 || half <= 0) return 0;
     const int n = T * half;
-    prism::rope_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, half, T, (float2*)table);
-    return (int)cudaPeekAtLastError();
+    return (int)prism::launch_kernel(prism::rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions,
+                                     inv_freq, half, T, (float2*)table);
+}
+
+// q/k/v as float32 partial sums [ks, T, (nh + 2 nkv) * hd] (+ bias): rotate, write q to q_out [T, nh * hd]
+// (row stride q_out_stride) and k, v to the cache.  Needs the table, head_dim % 8 == 0, rotary_dim % 16 == 0.
+PRISM_EXPORT int prism_rope_kv_write_partial(const float* parts, int ks, const void* bias, int bias_dtype, void* q_out,
+                                             int q_out_stride, int dtype, const int* positions, const int* tok_seg,
+                                             const float* table, int rotary_dim, void* kc, void* vc,
+                                             const int* block_table, int bt_width, int page_size, int num_pages,
+                                             int T, int nh, int nkv, int hd, int max_pos, int* err,
+                                             cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (table == nullptr || hd % 8 || rotary_dim % 16 || rotary_dim > hd || q_out_stride % 8 || ks < 1)
+        return (int)cudaErrorInvalidValue;
+    const int D = (nh + 2 * nkv) * hd;
+    const int items = (nh + nkv) * ((hd - rotary_dim / 2) / 8) + nkv * (hd / 8);
+    const int threads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+    const int bb = bias_dtype == PRISM_DTYPE_BF16;
+    if (dtype == PRISM_DTYPE_BF16)
+        return (int)prism::launch_kernel(prism::rope_kv_partial_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+                                         parts, ks, (size_t)T * D, D, bias, bb, (__nv_bfloat16*)q_out, q_out_stride,
+                                         positions, tok_seg, (const float2*)table, rotary_dim, (__nv_bfloat16*)kc,
+                                         (__nv_bfloat16*)vc, block_table, bt_width, page_size, num_pages, nh, nkv, hd,
+                                         max_pos, err);
+    return (int)prism::launch_kernel(prism::rope_kv_partial_kernel<float>, dim3(T), dim3(threads), 0, stream, parts, ks,
+                                     (size_t)T * D, D, bias, bb, (float*)q_out, q_out_stride, positions, tok_seg,
+                                     (const float2*)table, rotary_dim, (float*)kc, (float*)vc, block_table, bt_width,
+                                     page_size, num_pages, nh, nkv, hd, max_pos, err);
 }
 
 // `table` (optional): float2 [T, rotary_dim / 2] from prism_rope_table; with it, and with
@@ -189,16 +305,14 @@ PRISM_EXPORT int prism_rope_kv_write(void* q, void* k, const void* v, int dtype,
         const int items = (nh + nkv) * (hd / 2 / 8) + nkv * (hd / 8) + nkv * ((hd - rotary_dim) / 8);
         const int vthreads = items >= 256 ? 256 : (items + 31) / 32 * 32;
         if (dtype == PRISM_DTYPE_BF16)
-            prism::rope_kv_vec_kernel<__nv_bfloat16><<<T, vthreads, 0, stream>>>(
+            return (int)prism::launch_kernel(prism::rope_kv_vec_kernel<__nv_bfloat16>, dim3(T), dim3(vthreads), 0, stream,
                 (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, positions,
                 tok_seg, (const float2*)table, rotary_dim, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
                 block_table, bt_width, page_size, num_pages, nh, nkv, hd, max_pos, err);
-        else
-            prism::rope_kv_vec_kernel<float><<<T, vthreads, 0, stream>>>(
+        return (int)prism::launch_kernel(prism::rope_kv_vec_kernel<float>, dim3(T), dim3(vthreads), 0, stream,
                 (float*)q, (float*)k, (const float*)v, row_stride, positions, tok_seg,
                 (const float2*)table, rotary_dim, (float*)kc, (float*)vc, block_table, bt_width,
                 page_size, num_pages, nh, nkv, hd, max_pos, err);
-        return (int)cudaPeekAtLastError();
     }
     const int threads = 128;
     if (dtype == PRISM_DTYPE_BF16)

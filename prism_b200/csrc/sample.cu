@@ -15,6 +15,8 @@ constexpr int SAMPLE_THREADS = 512;
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ u, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     __shared__ float s_val[SAMPLE_THREADS];
     __shared__ int s_idx[SAMPLE_THREADS];

@@ -8,6 +8,8 @@ namespace prism {
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
@@ -20,6 +22,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // I % 8 == 0: a thread takes 8 neighbouring columns of one row (16-byte accesses for bf16).
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= I) return;

@@ -66,6 +66,7 @@ def lib():
                 fn = getattr(_lib, name)
                 fn.restype = ctypes.c_int
                 fn.argtypes = getattr(_Sig, name)
+        _lib.prism_set_pdl(0 if os.environ.get("PRISM_PDL", "1") == "0" else 1)
     return _lib
 
 
@@ -80,18 +81,21 @@ class _Sig:
     prism_embed = [_p, _p, _i, _p, _i, _i, _i, _p, _p]
     prism_add_rmsnorm = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _p, _i, _i, _p]
     prism_rope_table = [_p, _p, _i, _i, _p, _p]
+    prism_rope_kv_write_partial = [_p, _i, _p, _i, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i,
+                                   _i, _p, _p]
     prism_rope_kv_write = [_p, _p, _p, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i,
                            _i, _i, _p, _p]
     prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                _i, _f, _p, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
-                                   _p, _p, _i, _p, _p]
+                                   _p, _p, _i, _p, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
+    prism_set_pdl = [_i]
     prism_gemm_tcgen05_supported = [_i, _i, _i]
     prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]
     prism_gemv_bf16_supported = [_i, _i, _i]
@@ -390,6 +394,66 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: 
                                      hd, max_pos, _ptr(err), _stream()), "rope_kv_write")
 
 
+def rope_kv_write_partial(parts: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                          positions: torch.Tensor, tok_seg: torch.Tensor, table: torch.Tensor, rotary_dim: int,
+                          k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                          block_table: Optional[torch.Tensor], num_pages: int, max_pos: int, nkv: int,
+                          err: torch.Tensor):
+    """``rope_kv_write`` for a qkv projection that arrives as float32 partial
+    sums ``parts [k, T, (nh + 2 nkv) * hd]`` (+ ``bias``): the sum, the bias, the
+    rotation and the cache store in one kernel; rotated q goes to ``q_out [T, nh, hd]``."""
+    _cuda(parts, bias, q_out, positions, tok_seg, table, k_cache, v_cache, block_table)
+    ks, T, D = parts.shape
+    _, nh, hd = q_out.shape
+    assert parts.dtype == torch.float32 and parts.is_contiguous() and D == (nh + 2 * nkv) * hd
+    assert q_out.is_contiguous() and table.dtype == torch.float32 and table.shape == (T, rotary_dim // 2, 2)
+    P = W = 0
+    if k_cache is not None:
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == q_out.dtype
+        assert k_cache.shape[2:] == (nkv, hd)
+        P, W = k_cache.shape[1], block_table.shape[1]
+    _check(lib().prism_rope_kv_write_partial(_ptr(parts), ks, _ptr(bias), F32 if bias is None else _dt(bias),
+                                             _ptr(q_out), nh * hd, _dt(q_out), _ptr(positions), _ptr(tok_seg),
+                                             _ptr(table), rotary_dim, _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+                                             W, P, num_pages, T, nh, nkv, hd, max_pos, _ptr(err), _stream()),
+           "rope_kv_write_partial")
+
+
+def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], nh: int, nkv: int,
+                     hd: int, rot, cache) -> torch.Tensor:
+    """The front half of an attention layer: qkv projection (+ bias), rotary
+    encoding of q and k (``rot``: RotaryParams or None), store of k, v into the
+    cache plane.  Returns q ``[T, nh, hd]``.  For a few tokens the projection runs
+    K-split on the tensor-core GEMM and its partial sums are added, biased,
+    rotated and stored by one kernel."""
+    T = x.shape[0]
+    qs, kvs = nh * hd, nkv * hd
+    table = None
+    if rot is not None and rot.rotary_dim:
+        key = ("rotary_table", rot.inv_freq.data_ptr())          # one table per step for all layers
+        table = ctx.scratch.get(key)
+        if table is None:
+            table = ctx.scratch[key] = ctx.alloc((T, rot.rotary_dim // 2, 2), torch.float32)
+            rope_table(ctx.positions, rot.inv_freq, table)
+    kc, vc = (cache.k, cache.v) if cache.write else (None, None)
+    if table is not None and tc_gemm_ok(x, qkv_w) and hd % 8 == 0 and rot.rotary_dim % 16 == 0:
+        ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
+        if ks > 1:
+            parts = ctx.alloc((ks, T, qs + 2 * kvs), torch.float32)
+            gemm_tc(x, qkv_w, None, parts, EPI_PARTIAL, ksplit=ks)
+            q = ctx.alloc((T, nh, hd), x.dtype)
+            rope_kv_write_partial(parts, qkv_b, q, ctx.positions, ctx.tok_seg, table, rot.rotary_dim, kc, vc,
+                                  cache.block_table, cache.num_pages, ctx.max_positions, nkv, ctx.err)
+            return q
+    qkv = linear(x, qkv_w, qkv_b)
+    q = qkv[:, :qs].view(T, nh, hd)
+    k = qkv[:, qs:qs + kvs].view(T, nkv, hd)
+    v = qkv[:, qs + kvs:].view(T, nkv, hd)
+    rope_kv_write(q, k, v, ctx.positions, ctx.tok_seg, rot.inv_freq if rot else None, rot.rotary_dim if rot else 0,
+                  kc, vc, cache.block_table, cache.num_pages, ctx.max_positions, ctx.err, table=table)
+    return q
+
+
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
                       tok_seg: torch.Tensor, num_pages: int, window: Optional[int], scale: float,
@@ -437,8 +501,22 @@ NUM_SMS = 148
 FORCE_GENERIC_ATTENTION = os.environ.get("PRISM_ATTENTION", "") == "generic"
 
 
+_attn_counters = {}
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Per-(token, kv head) arrival counters of the decode attention; zero between launches."""
+    key = torch.device(device).index or 0
+    c = _attn_counters.get(key)
+    if c is None or c.numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention counters must be sized before graph capture (run one step eagerly first)")
+        c = _attn_counters[key] = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+    return c
+
+
 def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
-                          scale, nsplit, part_o, part_ml, err):
+                          scale, nsplit, part_o, part_ml, err, fused_merge: bool = True):
     """Tensor-core decode attention (one token per request) with the keys split
     over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
     ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results."""
@@ -453,9 +531,11 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                              _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                              int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                             int(nsplit), _ptr(err), _stream()), "attention_decode_bf16")
-    global launch_count
-    launch_count += 1          # the merge kernel
+                                             int(nsplit), _ptr(_decode_counters(q.device, T * nkv)) if fused_merge else None,
+                                             _ptr(err), _stream()), "attention_decode_bf16")
+    if not fused_merge:
+        global launch_count
+        launch_count += 1          # the merge kernel
 
 
 def attention_prefill_bf16(q, out, k_cache, v_cache, block_table, seg_start, cached_len, max_q_len,

@@ -53,24 +53,19 @@ class GQAAttention(Mixer):
 
     def forward(self, ctx, x, cache):
         T, qs, kvs = x.shape[0], self.q_size, self.kv_size
-        qkv = ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"))
-        q = qkv[:, :qs].view(T, self.nh, self.hd)
-        k = qkv[:, qs:qs + kvs].view(T, self.nkv, self.hd)
-        v = qkv[:, qs + kvs:].view(T, self.nkv, self.hd)
         rot = self.position.rotary() if self.position is not None else None
         if rot is None and self.position is not None:
+            # a position encoding that is not rotary: project, let it encode q and k, then store
+            qkv = ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"))
+            q = qkv[:, :qs].view(T, self.nh, self.hd)
+            k = qkv[:, qs:qs + kvs].view(T, self.nkv, self.hd)
+            v = qkv[:, qs + kvs:].view(T, self.nkv, self.hd)
             self.position.apply(ctx, q, k)
-        table = None
-        if rot is not None and rot.rotary_dim:
-            key = ("rotary_table", rot.inv_freq.data_ptr())        # one table per step for all layers
-            table = ctx.scratch.get(key)
-            if table is None:
-                table = ctx.scratch[key] = ctx.alloc((T, rot.rotary_dim // 2, 2), ops.torch.float32)
-                ops.rope_table(ctx.positions, rot.inv_freq, table)
-        ops.rope_kv_write(q, k, v, ctx.positions, ctx.tok_seg,
-                          rot.inv_freq if rot else None, rot.rotary_dim if rot else 0,
-                          cache.k if cache.write else None, cache.v if cache.write else None,
-                          cache.block_table, cache.num_pages, ctx.max_positions, ctx.err, table=table)
+            ops.rope_kv_write(q, k, v, ctx.positions, ctx.tok_seg, None, 0,
+                              cache.k if cache.write else None, cache.v if cache.write else None,
+                              cache.block_table, cache.num_pages, ctx.max_positions, ctx.err)
+        else:
+            q = ops.qkv_rotate_store(ctx, x, self.w["qkv_w"], self.w.get("qkv_b"), self.nh, self.nkv, self.hd, rot, cache)
         attn = ctx.alloc((T, qs), x.dtype)
         ops.attention(ctx, q, attn, cache, self.window, self.scale)
         return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))

@@ -313,6 +313,45 @@ def test_rope_kv_write(nh, nkv, hd, rd, P, dtype, use_table):
     assert int((kc != 0).any(dim=-1).any(dim=-1).sum()) <= T      # nothing else was written
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rd,P", [(28, 4, 128, 128, 256), (6, 3, 80, 32, 16), (5, 1, 48, 48, 8)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_rope_kv_write_from_partial_sums(nh, nkv, hd, rd, P, dtype, with_bias):
+    """q/k/v given as a stack of float32 partial sums plus bias: same q, same
+    cache contents as summing first and using the in-place kernel."""
+    ops = _ops()
+    T, S, W, ks = 11, 2, 30, 3
+    pages = S * W
+    D = (nh + 2 * nkv) * hd
+    parts = _rand((ks, T, D), torch.float32, 50)
+    bias = _rand((D,), dtype, 51) if with_bias else None
+    total = parts.sum(0) + (bias.float() if with_bias else 0)
+    tok_seg = torch.tensor([0] * 6 + [1] * 5, dtype=torch.int32, device=DEV)
+    positions = torch.tensor(list(range(40, 46)) + list(range(0, 5)), dtype=torch.int32, device=DEV)
+    bt = (torch.arange(S * W, dtype=torch.int32).view(S, W)).to(DEV)
+    theta = 1e4
+    inv = (1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))).to(DEV)
+    table = torch.empty(T, rd // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(positions, inv, table)
+    err = _err()
+    kc = torch.zeros(pages, P, nkv, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = torch.empty(T, nh, hd, dtype=dtype, device=DEV)
+    ops.rope_kv_write_partial(parts, bias, q, positions, tok_seg, table, rd, kc, vc, bt, pages, 1 << 20, nkv, err)
+    # reference: float32 sum, float32 rotation, one rounding
+    tq = total[:, :nh * hd].view(T, nh, hd)
+    tk = total[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    tv = total[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    rq, rk = ref_rope(tq, positions, inv, rd), ref_rope(tk, positions, inv, rd)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert int(err) == 0 and torch.allclose(q.float(), rq, atol=tol, rtol=tol)
+    for t in range(T):
+        s_, p_ = int(tok_seg[t]), int(positions[t])
+        page = int(bt[s_, p_ // P])
+        assert torch.allclose(kc[page, p_ % P].float(), rk[t], atol=tol, rtol=tol)
+        assert torch.allclose(vc[page, p_ % P].float(), tv[t], atol=tol, rtol=tol)
+
+
 def test_sample_greedy_and_temperature():
     ops = _ops()
     R, V = 9, 152064 // 8 + 5
@@ -388,7 +427,8 @@ DECODE_CASES = [
 
 
 @pytest.mark.parametrize("case", DECODE_CASES)
-def test_attention_decode_bf16(case):
+@pytest.mark.parametrize("fused_merge", [True, False])
+def test_attention_decode_bf16(case, fused_merge):
     ops = _ops()
     nh, nkv, hd, P, window, ctxs, nsplit = case
     c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=21)
@@ -397,11 +437,13 @@ def test_attention_decode_bf16(case):
     part_ml = torch.full((c.T, nh, nsplit, 2), float("nan"), device=DEV)
     err = _err()
     scale = hd ** -0.5
-    ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
-                              nsplit, part_o, part_ml, err)
     ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
-    assert int(err) == 0 and not torch.isnan(out.float()).any()
-    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+    for _ in range(2):                               # twice: the counters of the fused merge reset themselves
+        out.fill_(float("nan"))
+        ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
+                                  nsplit, part_o, part_ml, err, fused_merge=fused_merge)
+        assert int(err) == 0 and not torch.isnan(out.float()).any()
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
 PREFILL_CASES = [
