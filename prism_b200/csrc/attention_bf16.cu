@@ -16,7 +16,9 @@ PRISM_EXPORT int prism_attention_decode_bf16(const void* q, int q_stride, void* 
                                              int window, float scale, float* part_o, float* part_ml,
                                              int nsplit, int* counters, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535) return (int)cudaErrorInvalidValue;
+    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535 ||
+        (counters != nullptr && nsplit > 64))
+        return (int)cudaErrorInvalidValue;
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
              window, scale, part_o, part_ml, nsplit, err, stream, counters

@@ -45,7 +45,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit,
                    __nv_bfloat16* __restrict__ out, int out_stride, int* __restrict__ counters, int* err) {
-    pdl_wait();
     __shared__ int s_last;
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
@@ -85,22 +84,34 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         __threadfence();
         const float* bo = part_o + ((size_t)t * nh + (size_t)kvh * g) * nsplit * HD;
         const float* bml = part_ml + ((size_t)t * nh + (size_t)kvh * g) * nsplit * 2;
+        // all (max, sum) pairs at once, then one weight per (row, split), then the weighted sums:
+        // two rounds of independent loads instead of a chain of dependent ones
+        float* sm = reinterpret_cast<float*>(KV);          // [g * nsplit] maxima, later weights
+        float* sl = sm + 16 * 64;                          // [g * nsplit] sums
+        for (int i = tid; i < g * nsplit; i += ATT_THREADS) {
+            sm[i] = __ldcg(bml + 2 * i);
+            sl[i] = __ldcg(bml + 2 * i + 1);
+        }
+        __syncthreads();
+        if (tid < g) {
+            float M = -INFINITY, L = 0.f;
+            for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, sm[tid * nsplit + sp]);
+            const float Mu = M == -INFINITY ? 0.f : M;
+            for (int sp = 0; sp < nsplit; ++sp) L += sl[tid * nsplit + sp] * exp2_guard(sm[tid * nsplit + sp], Mu);
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            for (int sp = 0; sp < nsplit; ++sp) sm[tid * nsplit + sp] = exp2_guard(sm[tid * nsplit + sp], Mu) * inv;
+        }
+        __syncthreads();
         for (int i = tid; i < g * HD; i += ATT_THREADS) {
             const int r = i / HD, d = i % HD;
-            const float* ml = bml + (size_t)r * nsplit * 2;
-            float M = -INFINITY;
-            for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(ml + 2 * sp));
-            const float Mu = M == -INFINITY ? 0.f : M;
-            float L = 0.f, acc = 0.f;
-            for (int sp = 0; sp < nsplit; ++sp) {
-                const float f = exp2_guard(__ldcg(ml + 2 * sp), Mu);
-                L += __ldcg(ml + 2 * sp + 1) * f;
-                acc += __ldcg(bo + ((size_t)r * nsplit + sp) * HD + d) * f;
-            }
-            out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            float acc = 0.f;
+#pragma unroll 4
+            for (int sp = 0; sp < nsplit; ++sp) acc += __ldcg(bo + ((size_t)r * nsplit + sp) * HD + d) * sm[r * nsplit + sp];
+            out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(acc);
         }
     };
     if (t0 >= t1) {           // nothing for this split: an empty partial
+        pdl_wait();
         for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * nsplit * HD + i % HD] = 0.f;
         for (int r = tid; r < g; r += ATT_THREADS) {
             pml[(size_t)r * nsplit * 2] = -INFINITY;
@@ -111,12 +122,16 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         return;
     }
 
-    // Q rows of this kv head's group (rows >= g are zero)
-    for (int i = tid; i < 16 * (HD / 8); i += ATT_THREADS) {
-        const int r = i / (HD / 8), c = i % (HD / 8);
-        cp_async16(Qs + r * STRIDE + c * 8, q + (size_t)t * q_stride + ((size_t)kvh * g + (r < g ? r : 0)) * HD + c * 8, r < g);
-    }
+    // Keys and values of earlier steps are in the cache already; only the tile that holds this
+    // step's own position (written by the kernel before this one) and q must wait for the kernels
+    // before this one.  Everything else is requested at once, while those kernels still run.
+    const int own_tile = hi / ATT_TILE;
+    bool waited = false;
     auto load_tile = [&](int tile, int stage) {
+        if (tile == own_tile && !waited) {
+            pdl_wait();
+            waited = true;
+        }
         __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
         load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
                                                 page_shift, num_pages, nkv, kvh, err);
@@ -125,6 +140,18 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int s = 0; s < DEC_STAGES - 1; ++s) {
         if (t0 + s < t1) load_tile(t0 + s, s);
         cp_async_commit();
+    }
+    if (!waited) {
+        pdl_wait();
+        waited = true;
+    }
+    // Q rows of this kv head's group (rows >= g are zero), with plain loads: visible after the
+    // first barrier of the loop below
+    for (int i = tid; i < 16 * (HD / 8); i += ATT_THREADS) {
+        const int r = i / (HD / 8), c = i % (HD / 8);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < g) v = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + ((size_t)kvh * g + r) * HD + c * 8);
+        *reinterpret_cast<uint4*>(Qs + r * STRIDE + c * 8) = v;
     }
 
     uint32_t qf[HD / 16][4];

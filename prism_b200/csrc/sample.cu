@@ -80,7 +80,75 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     if (tid == 0) out[row] = s_idx[0] >= 0 ? s_idx[0] : amax;
 }
 
+// Greedy only, many blocks per row: block (b, row) finds the best of its slice of the
+// vocabulary and leaves (value, index) in `part`; the block that arrives last at the row's
+// counter reduces the slices (lowest index on ties) and writes the token.  Nobody waits.
+constexpr int ARGMAX_THREADS = 256;
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_split_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict__ part_val,
+                    int* __restrict__ part_idx, int* __restrict__ counters, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float s_val[ARGMAX_THREADS];
+    __shared__ int s_idx[ARGMAX_THREADS];
+    __shared__ int s_last;
+    const int nb = gridDim.x, b = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+    const int per = ((V + nb - 1) / nb + 3) & ~3;
+    const int c0 = min(b * per, V), c1 = min(c0 + per, V);
+    const float* x = logits + (size_t)row * ld;
+    float best = -INFINITY;
+    int besti = V;
+    for (int i = c0 + tid; i < c1; i += ARGMAX_THREADS) {
+        const float v = x[i];
+        if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+    }
+    auto reduce = [&]() {
+        s_val[tid] = best;
+        s_idx[tid] = besti;
+        __syncthreads();
+        for (int o = ARGMAX_THREADS / 2; o > 0; o >>= 1) {
+            if (tid < o) {
+                const float v = s_val[tid + o];
+                const int i = s_idx[tid + o];
+                if (v > s_val[tid] || (v == s_val[tid] && i < s_idx[tid])) { s_val[tid] = v; s_idx[tid] = i; }
+            }
+            __syncthreads();
+        }
+    };
+    reduce();
+    if (tid == 0) {
+        part_val[(size_t)row * nb + b] = s_val[0];
+        part_idx[(size_t)row * nb + b] = s_idx[0];
+        __threadfence();
+        const int old = atomicAdd(&counters[row], 1);
+        s_last = old == nb - 1;
+        if (s_last) counters[row] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY;
+    besti = V;
+    if (tid < nb) {
+        best = __ldcg(&part_val[(size_t)row * nb + tid]);
+        besti = __ldcg(&part_idx[(size_t)row * nb + tid]);
+    }
+    reduce();
+    if (tid == 0) out[row] = s_idx[0] < V ? s_idx[0] : 0;
+}
+
 }  // namespace prism
+
+// All rows greedy, several blocks per row.  part_val/part_idx: R * nb entries; counters: R ints, zero
+// before the first launch (the kernel leaves them zero).  nb <= 256.
+PRISM_EXPORT int prism_argmax_split(const float* logits, int ld, int R, int V, int nb, float* part_val,
+                                    int* part_idx, int* counters, int* out, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (nb < 1 || nb > prism::ARGMAX_THREADS || R > 65535) return (int)cudaErrorInvalidValue;
+    return (int)prism::launch_kernel(prism::argmax_split_kernel, dim3(nb, R), dim3(prism::ARGMAX_THREADS), 0, stream,
+                                     logits, ld, V, part_val, part_idx, counters, out);
+}
 
 // temperature and u may be null: all rows greedy.
 PRISM_EXPORT int prism_sample(const float* logits, int ld, int R, int V, const float* temperature,

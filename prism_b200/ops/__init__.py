@@ -95,6 +95,7 @@ class _Sig:
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
+    prism_argmax_split = [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_set_pdl = [_i]
     prism_gemm_tcgen05_supported = [_i, _i, _i]
     prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]
@@ -436,7 +437,7 @@ def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[
             table = ctx.scratch[key] = ctx.alloc((T, rot.rotary_dim // 2, 2), torch.float32)
             rope_table(ctx.positions, rot.inv_freq, table)
     kc, vc = (cache.k, cache.v) if cache.write else (None, None)
-    if table is not None and tc_gemm_ok(x, qkv_w) and hd % 8 == 0 and rot.rotary_dim % 16 == 0:
+    if QKV_PARTIAL and table is not None and tc_gemm_ok(x, qkv_w) and hd % 8 == 0 and rot.rotary_dim % 16 == 0:
         ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
         if ks > 1:
             parts = ctx.alloc((ks, T, qs + 2 * kvs), torch.float32)
@@ -482,6 +483,9 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor):
     _check(lib().prism_swiglu(_ptr(gu), _ptr(out), _dt(gu), T, I2 // 2, _stream()), "swiglu")
 
 
+_argmax_ws = {}
+
+
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optional[torch.Tensor],
            out: torch.Tensor):
     """Per row: argmax if its temperature <= 0, else inverse-CDF sampling of
@@ -489,6 +493,19 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optiona
     _cuda(logits, temperature, u, out)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     R, V = logits.shape
+    if temperature is None and V >= 8192 and R <= 4096 and not torch.cuda.is_current_stream_capturing():
+        # greedy over a large vocabulary: many blocks per row
+        key = torch.device(logits.device).index or 0
+        ws = _argmax_ws.get(key)
+        nb = 32
+        if ws is None or ws[0].numel() < R * nb:
+            n = max(R * nb, 4096 * nb)
+            ws = _argmax_ws[key] = (torch.empty(n, dtype=torch.float32, device=logits.device),
+                                    torch.empty(n, dtype=torch.int32, device=logits.device),
+                                    torch.zeros(4096, dtype=torch.int32, device=logits.device))
+        _check(lib().prism_argmax_split(_ptr(logits), logits.stride(0), R, V, nb, _ptr(ws[0]), _ptr(ws[1]),
+                                        _ptr(ws[2]), _ptr(out), _stream()), "argmax_split")
+        return
     _check(lib().prism_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(u),
                               _ptr(out), _stream()), "sample")
 
@@ -515,8 +532,14 @@ def _decode_counters(device, n: int) -> torch.Tensor:
     return c
 
 
+# merging the splits inside the attention kernel (last CTA) measured slower on B200 than a second small
+# kernel launched with programmatic dependent launch; it stays available and tested
+FUSED_MERGE = os.environ.get("PRISM_ATTN_FUSED_MERGE", "0") == "1"
+QKV_PARTIAL = os.environ.get("PRISM_QKV_PARTIAL", "1") != "0"
+
+
 def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
-                          scale, nsplit, part_o, part_ml, err, fused_merge: bool = True):
+                          scale, nsplit, part_o, part_ml, err, fused_merge: Optional[bool] = None):
     """Tensor-core decode attention (one token per request) with the keys split
     over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
     ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results."""
@@ -527,6 +550,7 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
     assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1
     assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
+    fused_merge = FUSED_MERGE if fused_merge is None else fused_merge
     _check(lib().prism_attention_decode_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache),
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                              _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,

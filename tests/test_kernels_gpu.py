@@ -358,10 +358,18 @@ def test_sample_greedy_and_temperature():
     logits = _rand((R, V), torch.float32, 12, 3.0)
     logits[3, 100] = logits[3, 7] = logits[3].max() + 1           # a tie: the lowest index wins
     out = torch.empty(R, dtype=torch.int32, device=DEV)
-    ops.sample(logits, None, None, out)
+    ops.sample(logits, None, None, out)                       # V >= 8192: the many-blocks-per-row kernel
     ref = logits.argmax(-1)
     ref[3] = 7
     assert torch.equal(out.long(), ref)
+    ops.sample(logits, None, None, out)                       # again: its counters reset themselves
+    assert torch.equal(out.long(), ref)
+    small = logits[:, :1000].contiguous()                     # small vocabulary: one block per row
+    small[3, 7] = small[3, 100] = small[3].max() + 1
+    ops.sample(small, None, None, out)
+    rs = small.argmax(-1)
+    rs[3] = 7
+    assert torch.equal(out.long(), rs)
     temps = torch.tensor([0.7, 0.0, 1.3, 0.2, 1.0, 0.5, 2.0, 0.9, 1.1], device=DEV)
     us = torch.tensor([0.0, 0.5, 0.999999, 0.3, 0.25, 0.75, 0.5, 0.1, 0.9], device=DEV)
     ops.sample(logits, temps, us, out)
