@@ -19,6 +19,8 @@
 // shared memory, 3 stages deep (decode) or double-buffered (prefill).
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "mma_helpers.cuh"
 
 namespace prism {
@@ -36,7 +38,10 @@ __device__ __forceinline__ float exp2_guard(float x, float m) {   // exp2(x - m)
 // ---------------------------------------------------------------------------
 // decode
 // ---------------------------------------------------------------------------
-template <int HD>
+// CLUSTER: the CTAs of one (token, kv head) - one per split - form a thread-block cluster and merge
+// their partial results through distributed shared memory: no partials in global memory, no second
+// kernel.  At most 8 splits (the portable cluster size).
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
@@ -110,7 +115,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(acc);
         }
     };
-    if (t0 >= t1) {           // nothing for this split: an empty partial
+    if (!CLUSTER && t0 >= t1) {           // nothing for this split: an empty partial
         pdl_wait();
         for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * nsplit * HD + i % HD] = 0.f;
         for (int r = tid; r < g; r += ATT_THREADS) {
@@ -238,6 +243,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float* red_o = reinterpret_cast<float*>(KV);                 // [4][16][HD]
     float* red_m = red_o + 4 * 16 * HD;                          // [4][16]
     float* red_l = red_m + 4 * 16;                               // [4][16]
+    float* fin_o = red_l + 4 * 16;                               // [16][HD]  this split's merged partial (CLUSTER)
+    float* fin_m = fin_o + 16 * HD;                              // [16]
+    float* fin_l = fin_m + 16;                                   // [16]
     const int r0 = lane >> 2;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
@@ -264,13 +272,57 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             acc += red_o[((size_t)w * 16 + r) * HD + d] * f;
             L += red_l[w * 16 + r] * f;
         }
-        po[(size_t)r * nsplit * HD + d] = acc;
-        if (d == 0) {
-            pml[(size_t)r * nsplit * 2] = M;
-            pml[(size_t)r * nsplit * 2 + 1] = L;
+        if (CLUSTER) {
+            fin_o[r * HD + d] = acc;
+            if (d == 0) { fin_m[r] = M; fin_l[r] = L; }
+        } else {
+            po[(size_t)r * nsplit * HD + d] = acc;
+            if (d == 0) {
+                pml[(size_t)r * nsplit * 2] = M;
+                pml[(size_t)r * nsplit * 2 + 1] = L;
+            }
         }
     }
-    merge_if_last();
+    if (!CLUSTER) {
+        merge_if_last();
+        return;
+    }
+    // every split's (max, sum, output) is in its CTA's shared memory: each CTA of the cluster merges
+    // its share of the g * HD outputs, reading the others' partials through distributed shared memory
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int rank = (int)cluster.block_rank();
+    const int chunk = (g * HD + nsplit - 1) / nsplit;
+    const int i1 = min(g * HD, (rank + 1) * chunk);
+    for (int i = rank * chunk + tid; i < i1; i += ATT_THREADS) {
+        const int r = i / HD, d = i % HD;
+        float ms[8], ls[8], os[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+            if (sp < nsplit) {
+                const float* rm = cluster.map_shared_rank(fin_m, sp);
+                const float* rl = cluster.map_shared_rank(fin_l, sp);
+                const float* ro = cluster.map_shared_rank(fin_o, sp);
+                ms[sp] = rm[r]; ls[sp] = rl[r]; os[sp] = ro[r * HD + d];
+            } else {
+                ms[sp] = -INFINITY; ls[sp] = 0.f; os[sp] = 0.f;
+            }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, ms[sp]);
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+            const float f = exp2_guard(ms[sp], Mu);
+            L += ls[sp] * f;
+            acc += os[sp] * f;
+        }
+        out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+    cluster.sync();          // nobody leaves while its shared memory may still be read
 }
 
 // merge the splits: out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
@@ -469,11 +521,32 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
                   const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
                   int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
-                  int* err, cudaStream_t stream, int* counters = nullptr) {
-    static_assert(dec_smem<HD>() >= (size_t)(4 * 16 * HD + 128) * sizeof(float) + 16 * TileRow<HD>::STRIDE * 2, "merge scratch must fit");
-    auto kern = attn_decode_kernel<HD>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
+                  int* err, cudaStream_t stream, int* counters = nullptr, bool use_cluster = false) {
+    static_assert(dec_smem<HD>() >= (size_t)(5 * 16 * HD + 128 + 32) * sizeof(float) + 16 * TileRow<HD>::STRIDE * 2, "merge scratch must fit");
     dim3 grid(nsplit, nkv, T);
+    if (counters == nullptr && use_cluster && nsplit >= 2 && nsplit <= 8) {
+        auto kc_ = attn_decode_kernel<HD, true>;
+        cudaFuncSetAttribute(kc_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(ATT_THREADS);
+        cfg.dynamicSmemBytes = dec_smem<HD>();
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = nsplit;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        return (int)cudaLaunchKernelEx(&cfg, kc_, q, q_stride, kc, vc, bt, bt_width, positions, tok_seg, nh, nkv, page_size,
+                                       page_shift_of(page_size), num_pages, window, scale * 1.4426950408889634f, part_o,
+                                       part_ml, nsplit, out, out_stride, (int*)nullptr, err);
+    }
+    auto kern = attn_decode_kernel<HD, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
     cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
                                    positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
                                    scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, counters, err);

@@ -89,7 +89,7 @@ class _Sig:
                                _i, _f, _p, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
-                                   _p, _p, _i, _p, _p, _p]
+                                   _p, _p, _i, _p, _i, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
@@ -535,11 +535,15 @@ def _decode_counters(device, n: int) -> torch.Tensor:
 # merging the splits inside the attention kernel (last CTA) measured slower on B200 than a second small
 # kernel launched with programmatic dependent launch; it stays available and tested
 FUSED_MERGE = os.environ.get("PRISM_ATTN_FUSED_MERGE", "0") == "1"
+# merging the splits through distributed shared memory in a thread-block cluster: correct and tested, but
+# measured slightly slower at decode sizes than partials + a merge kernel under programmatic dependent launch
+CLUSTER_MERGE = os.environ.get("PRISM_ATTN_CLUSTER", "0") == "1"
 QKV_PARTIAL = os.environ.get("PRISM_QKV_PARTIAL", "1") != "0"
 
 
 def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
-                          scale, nsplit, part_o, part_ml, err, fused_merge: Optional[bool] = None):
+                          scale, nsplit, part_o, part_ml, err, fused_merge: Optional[bool] = None,
+                          cluster: Optional[bool] = None):
     """Tensor-core decode attention (one token per request) with the keys split
     over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
     ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results."""
@@ -551,13 +555,15 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
     assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
     fused_merge = FUSED_MERGE if fused_merge is None else fused_merge
+    cluster = CLUSTER_MERGE if cluster is None else cluster
+    cluster = bool(cluster) and not fused_merge and 2 <= nsplit <= 8
     _check(lib().prism_attention_decode_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache),
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                              _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                              int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
                                              int(nsplit), _ptr(_decode_counters(q.device, T * nkv)) if fused_merge else None,
-                                             _ptr(err), _stream()), "attention_decode_bf16")
-    if not fused_merge:
+                                             int(cluster), _ptr(err), _stream()), "attention_decode_bf16")
+    if not fused_merge and not cluster:
         global launch_count
         launch_count += 1          # the merge kernel
 
@@ -590,7 +596,10 @@ def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> i
     tiles = max(1, (span + 63) // 64)
     fill = (2 * NUM_SMS) // max(1, T * nkv)          # one wave of two CTAs per SM, not a little more
     balance = -(-tiles // 8)                          # at most ~8 tiles per CTA so that SMs finish together
-    return max(1, min(tiles, 64, max(fill, balance)))
+    n = max(1, min(tiles, 64, max(fill, balance)))
+    if CLUSTER_MERGE and 8 < n <= 12:
+        n = 8                                         # one cluster of 8 beats a few more splits merged through memory
+    return n
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[int], scale: float):

@@ -428,6 +428,7 @@ DECODE_CASES = [
     (28, 4, 128, 256, None, [2048, 1, 0, 255, 256, 257, 4000], 10),
     (28, 4, 128, 64, None, [63, 64, 65, 1000], 1),
     (8, 8, 64, 16, None, [5, 300, 129], 3),
+    (28, 4, 128, 256, None, [2100, 2047, 1, 64, 700, 4095, 33, 1000], 8),
     (16, 1, 64, 32, 100, [99, 100, 101, 700, 3], 7),
     (14, 2, 128, 8, 64, [1500, 64, 63], 64),
     (40, 8, 128, 256, None, [3000], 33),
@@ -435,7 +436,7 @@ DECODE_CASES = [
 
 
 @pytest.mark.parametrize("case", DECODE_CASES)
-@pytest.mark.parametrize("fused_merge", [True, False])
+@pytest.mark.parametrize("fused_merge", ["last_cta", "kernel", "cluster"])
 def test_attention_decode_bf16(case, fused_merge):
     ops = _ops()
     nh, nkv, hd, P, window, ctxs, nsplit = case
@@ -449,7 +450,8 @@ def test_attention_decode_bf16(case, fused_merge):
     for _ in range(2):                               # twice: the counters of the fused merge reset themselves
         out.fill_(float("nan"))
         ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
-                                  nsplit, part_o, part_ml, err, fused_merge=fused_merge)
+                                  nsplit, part_o, part_ml, err, fused_merge=fused_merge == "last_cta",
+                                  cluster=fused_merge == "cluster")
         assert int(err) == 0 and not torch.isnan(out.float()).any()
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
