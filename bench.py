@@ -153,6 +153,22 @@ def run(args):
         runner.check_errors()
         return ms, launches, ctx_mean, ck
 
+    if args.quick == "prefill":
+        # one prompt of PROMPT tokens, a few times, for profilers
+        p = prompts(1)[0]
+        times = []
+        for i in range(max(2, K)):
+            runner.begin_request("pf")
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step([Segment("pf", p, [PROMPT - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            runner.end_request("pf")
+        print(json.dumps({"quick": "prefill", "layers": cfg["num_hidden_layers"], "tokens": PROMPT,
+                          "ms": round(min(times[1:]), 3)}))
+        return
     if args.quick:
         # decode only, for profilers: no prefill timing, no other batch sizes, no end-to-end run
         ms, launches, ctx_mean, _ = decode_bench(B, K, Wm)
@@ -231,12 +247,13 @@ def run(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
-    ap.add_argument("--quick", action="store_true", help="decode at --batch only (short runs under a profiler)")
+    ap.add_argument("--quick", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                    help="only the decode steps at --batch, or only the prefill (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

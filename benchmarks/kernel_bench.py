@@ -110,7 +110,7 @@ def bench_attn_decode(args):
     kc, vc, bt, q, pos, seg, _, _, n_pages = paged_case(B, ctx - 1, 1)
     out = torch.empty(B, NH * HD, device=DEV, dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ns = ops.decode_splits(B, NKV, args.bound or ctx, None)
+    ns = args.splits or ops.decode_splits(B, NKV, args.bound or ctx, None)
     po = torch.empty(B, NH, ns, HD, device=DEV)
     pml = torch.empty(B, NH, ns, 2, device=DEV)
     fn = lambda: ops.attention_decode_bf16(q, out, kc, vc, bt, pos, seg, n_pages, None, HD ** -0.5, ns, po, pml, err)
@@ -173,6 +173,7 @@ if __name__ == "__main__":
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--bound", type=int, default=0, help="context bound used to choose the splits")
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: CTAs per (token, kv head); 0 = the engine's choice")
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--once", action="store_true")
     a = ap.parse_args()

@@ -27,12 +27,21 @@ namespace prism {
 
 constexpr int ATT_TILE = 64;       // keys per tile
 constexpr int ATT_THREADS = 128;   // 4 warps
-constexpr int DEC_STAGES = 3;
+#ifndef PRISM_DEC_STAGES
+#define PRISM_DEC_STAGES 3
+#endif
+constexpr int DEC_STAGES = PRISM_DEC_STAGES;
 constexpr int PRE_STAGES = 2;
 constexpr int PRE_ROWS = 64;       // query rows per CTA
 
 __device__ __forceinline__ float exp2_guard(float x, float m) {   // exp2(x - m), 0 when x is -inf
     return x == -INFINITY ? 0.f : exp2f(x - m);
+}
+// exp2(x - m) for finite m: the hardware approximation (2 ulp), which gives 0 for x = -inf by itself
+__device__ __forceinline__ float exp2_fast(float x, float m) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x - m));
+    return y;
 }
 
 // ---------------------------------------------------------------------------
@@ -52,10 +61,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    __nv_bfloat16* __restrict__ out, int out_stride, int* __restrict__ counters, int* err) {
     __shared__ int s_last;
     constexpr int STRIDE = TileRow<HD>::STRIDE;
-    constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
+    constexpr int SUB_ELEMS = 16 * STRIDE;                           // one warp's 16 keys of a tile
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][STRIDE]
-    __nv_bfloat16* KV = Qs + 16 * STRIDE;                            // [stage][K|V][64][STRIDE]
+    __nv_bfloat16* KV = Qs + 16 * STRIDE;                            // [warp][stage][K|V][16][STRIDE]
 
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -137,9 +146,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             pdl_wait();
             waited = true;
         }
-        __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
-        load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
-                                                page_shift, num_pages, nkv, kvh, err);
+        // each warp streams the 16 keys of the tile that it will multiply, into stages of its own:
+        // the warps of a CTA never wait for one another inside the loop
+        __nv_bfloat16* ks = KV + ((size_t)(warp * DEC_STAGES + stage) * 2) * SUB_ELEMS;
+        load_kv_tile<HD, 16, 32>(ks, ks + SUB_ELEMS, kc, vc, bt, tile * ATT_TILE + warp * 16, lo, hi, page_size,
+                                 page_shift, num_pages, nkv, kvh, err, lane);
     };
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; ++s) {
@@ -158,6 +169,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (r < g) v = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + ((size_t)kvh * g + r) * HD + c * 8);
         *reinterpret_cast<uint4*>(Qs + r * STRIDE + c * 8) = v;
     }
+    __syncthreads();
 
     uint32_t qf[HD / 16][4];
     float o[HD / 8][4];
@@ -165,20 +177,18 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int mat = lane >> 3, lr = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], Qs + (lr + (mat & 1) * 8) * STRIDE + ks * 16 + (mat >> 1) * 8);
 
     for (int tile = t0; tile < t1; ++tile) {
         const int it = tile - t0;
         if (tile + DEC_STAGES - 1 < t1) load_tile(tile + DEC_STAGES - 1, (it + DEC_STAGES - 1) % DEC_STAGES);
         cp_async_commit();
         cp_async_wait<DEC_STAGES - 1>();
-        __syncthreads();
-        if (it == 0) {
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks)
-                ldmatrix_x4(qf[ks], Qs + (lr + (mat & 1) * 8) * STRIDE + ks * 16 + (mat >> 1) * 8);
-        }
-        const __nv_bfloat16* Ks = KV + (size_t)(it % DEC_STAGES) * 2 * TILE_ELEMS + warp * 16 * STRIDE;
-        const __nv_bfloat16* Vs = Ks + TILE_ELEMS;
+        __syncwarp();
+        const __nv_bfloat16* Ks = KV + ((size_t)(warp * DEC_STAGES + it % DEC_STAGES) * 2) * SUB_ELEMS;
+        const __nv_bfloat16* Vs = Ks + SUB_ELEMS;
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -187,15 +197,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_bf16_16816(s[0], qf[ks], b[0], b[1]);
             mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
         }
-        // mask, scale, online softmax over this warp's 16 keys (rows lane/4 and lane/4 + 8)
+        // mask (only a tile that crosses lo or hi needs it), scale, online softmax over this warp's
+        // 16 keys (rows lane/4 and lane/4 + 8)
         const int key0 = tile * ATT_TILE + warp * 16 + (lane & 3) * 2;
+        const bool edge = tile * ATT_TILE < lo || tile * ATT_TILE + ATT_TILE - 1 > hi;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + nt * 8 + (e & 1);
-                const float v = (key >= lo && key <= hi) ? s[nt][e] * scale_log2 : -INFINITY;
+                const float v = (!edge || (key >= lo && key <= hi)) ? s[nt][e] * scale_log2 : -INFINITY;
                 s[nt][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -205,8 +217,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_run[r], mx[r]);
-            mu[r] = m_new == -INFINITY ? 0.f : m_new;
-            corr[r] = exp2_guard(m_run[r], mu[r]);
+            mu[r] = m_new == -INFINITY ? 0.f : m_new;       // finite, so exp2_fast(-inf, mu) = 0
+            corr[r] = exp2_fast(m_run[r], mu[r]);
             m_run[r] = m_new;
             l_run[r] *= corr[r];
         }
@@ -214,7 +226,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float p = exp2_guard(s[nt][e], mu[e >> 1]);
+                const float p = exp2_fast(s[nt][e], mu[e >> 1]);
                 s[nt][e] = p;
                 l_run[e >> 1] += p;
             }
@@ -229,10 +241,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_bf16_16816(o[2 * j], pa, b[0], b[1]);
             mma_bf16_16816(o[2 * j + 1], pa, b[2], b[3]);
         }
-        __syncthreads();
+        __syncwarp();       // the stage is free for this warp's next load
     }
     cp_async_wait<0>();
     pdl_trigger_gemm();     // the keys are read: the next kernel may start its prologue
+    __syncthreads();        // every warp is out of its loop: the stage buffers become merge scratch
 
     // merge the four warps' partials through shared memory
 #pragma unroll
@@ -351,7 +364,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 // prefill / portions
 // ---------------------------------------------------------------------------
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(ATT_THREADS, 3)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                     int out_stride, const __nv_bfloat16* __restrict__ kc,
                     const __nv_bfloat16* __restrict__ vc, const int* __restrict__ block_table,
@@ -364,11 +377,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     constexpr int TILE_ELEMS = ATT_TILE * STRIDE;
     const int seg = blockIdx.z, h = blockIdx.y;
     const int s0 = seg_start[seg], qlen = seg_start[seg + 1] - s0;
-    const int q0 = blockIdx.x * PRE_ROWS;
+    // later query tiles see more keys: they are started first so that no SM is left with a long tile at the end
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * PRE_ROWS;
     if (q0 >= qlen) return;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [64][STRIDE]
-    __nv_bfloat16* KV = Qs + PRE_ROWS * STRIDE;                      // [stage][K|V][64][STRIDE]
+    __nv_bfloat16* KV = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [stage][K|V][64][STRIDE]
+    __nv_bfloat16* Qs = KV + 2 * TILE_ELEMS;                         // q passes through stage 1's K buffer on its
+                                                                     // way to registers, before that stage is first used
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rows = min(PRE_ROWS, qlen - q0);
@@ -388,8 +403,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     auto load_tile = [&](int tile, int stage) {
         __nv_bfloat16* ks = KV + (size_t)stage * 2 * TILE_ELEMS;
         load_kv_tile<HD, ATT_TILE, ATT_THREADS>(ks, ks + TILE_ELEMS, kc, vc, bt, tile * ATT_TILE, lo, hi, page_size,
-                                                page_shift, num_pages, nkv, kvh, err);
+                                                page_shift, num_pages, nkv, kvh, err, threadIdx.x);
     };
+    cp_async_commit();
     load_tile(t0, 0);
     cp_async_commit();
 
@@ -400,6 +416,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int mat = lane >> 3, lr = lane & 7;
     const int p_row[2] = {pos0 + warp * 16 + (lane >> 2), pos0 + warp * 16 + (lane >> 2) + 8};
+    cp_async_wait<1>();            // q has landed (the first tile may still be on its way)
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], Qs + (warp * 16 + lr + (mat & 1) * 8) * STRIDE + ks * 16 + (mat >> 1) * 8);
+    __syncthreads();               // stage 1 may now receive the second tile
 
     for (int tile = t0; tile < t1; ++tile) {
         const int it = tile - t0;
@@ -407,11 +429,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (it == 0) {
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks)
-                ldmatrix_x4(qf[ks], Qs + (warp * 16 + lr + (mat & 1) * 8) * STRIDE + ks * 16 + (mat >> 1) * 8);
-        }
         const __nv_bfloat16* Ks = KV + (size_t)(it % PRE_STAGES) * 2 * TILE_ELEMS;
         const __nv_bfloat16* Vs = Ks + TILE_ELEMS;
         // a warp whose 16 rows all sit before this tile's first key has nothing to do here
@@ -431,26 +448,41 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
                 }
             }
             const int key0 = tile * ATT_TILE + (lane & 3) * 2;
+            // only a tile that crosses the diagonal, the window's edge or the first key needs the mask
+            const int row_lo = pos0 + warp * 16, row_hi = row_lo + 15;
+            const bool edge = tile * ATT_TILE + ATT_TILE - 1 > row_lo || tile * ATT_TILE < lo ||
+                              (window > 0 && tile * ATT_TILE <= row_hi - window);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (edge) {
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+                for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + nt * 8 + (e & 1);
-                    const int p = p_row[e >> 1];
-                    const bool vis = key <= p && key >= lo && (window <= 0 || key > p - window);
-                    const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
-                    s[nt][e] = v;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + nt * 8 + (e & 1);
+                        const int p = p_row[e >> 1];
+                        const bool vis = key <= p && key >= lo && (window <= 0 || key > p - window);
+                        const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
+                        s[nt][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float v = s[nt][e] * scale_log2;
+                        s[nt][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+            }
             float corr[2], mu[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                mu[r] = m_new == -INFINITY ? 0.f : m_new;
-                corr[r] = exp2_guard(m_run[r], mu[r]);
+                mu[r] = m_new == -INFINITY ? 0.f : m_new;       // finite, so exp2_fast(-inf, mu) = 0
+                corr[r] = exp2_fast(m_run[r], mu[r]);
                 m_run[r] = m_new;
                 l_run[r] *= corr[r];
             }
@@ -458,7 +490,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bflo
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p = exp2_guard(s[nt][e], mu[e >> 1]);
+                    const float p = exp2_fast(s[nt][e], mu[e >> 1]);
                     s[nt][e] = p;
                     l_run[e >> 1] += p;
                 }
@@ -513,7 +545,7 @@ template <int HD> constexpr size_t dec_smem() {
     return (size_t)(16 + DEC_STAGES * 2 * ATT_TILE) * TileRow<HD>::STRIDE * sizeof(__nv_bfloat16);
 }
 template <int HD> constexpr size_t pre_smem() {
-    return (size_t)(PRE_ROWS + PRE_STAGES * 2 * ATT_TILE) * TileRow<HD>::STRIDE * sizeof(__nv_bfloat16);
+    return (size_t)(PRE_STAGES * 2 * ATT_TILE) * TileRow<HD>::STRIDE * sizeof(__nv_bfloat16);
 }
 
 template <int HD>

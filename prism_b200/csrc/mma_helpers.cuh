@@ -53,21 +53,37 @@ template <int HD> struct TileRow { static constexpr int STRIDE = HD + 8; };
 // is the same for K and V and is computed once.  Keys outside [lo, hi] are
 // zero-filled.  A page id outside the pool is reported and the row
 // zero-filled.  page_shift = log2(page_size) when that is a power of two, else -1.
+// THREADS threads (a CTA or one warp) load together; tid is the caller's index among them.
 template <int HD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
                                              const __nv_bfloat16* __restrict__ kcache,
                                              const __nv_bfloat16* __restrict__ vcache,
                                              const int* __restrict__ bt, int first_key, int lo, int hi,
                                              int page_size, int page_shift, int num_pages, int nkv, int kvh,
-                                             int* err) {
+                                             int* err, int tid) {
     constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
     constexpr int ROW_STEP = THREADS / CHUNKS;
     static_assert(THREADS % CHUNKS == 0 && ROWS % ROW_STEP == 0, "tile shape");
-    const int c = threadIdx.x % CHUNKS;
+    const int c = tid % CHUNKS;                    // tid: index of this thread among the THREADS that load
     const size_t row_elems = (size_t)nkv * HD;
     const size_t head_off = (size_t)kvh * HD + c * 8;
+    // Fast path: a tile that lies in one page and wholly inside [lo, hi]: one table lookup, then
+    // rows at a constant stride.
+    if (page_shift >= 0 && (first_key >> page_shift) == ((first_key + ROWS - 1) >> page_shift) && first_key >= lo &&
+        first_key + ROWS - 1 <= hi) {
+        const int page = bt[first_key >> page_shift];
+        if (page >= 0 && page < num_pages) {
+            const size_t base = ((size_t)page * page_size + (first_key & (page_size - 1))) * row_elems + head_off;
 #pragma unroll
-    for (int r = threadIdx.x / CHUNKS; r < ROWS; r += ROW_STEP) {
+            for (int r = tid / CHUNKS; r < ROWS; r += ROW_STEP) {
+                cp_async16(ks + r * TileRow<HD>::STRIDE + c * 8, kcache + base + (size_t)r * row_elems, true);
+                cp_async16(vs + r * TileRow<HD>::STRIDE + c * 8, vcache + base + (size_t)r * row_elems, true);
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int r = tid / CHUNKS; r < ROWS; r += ROW_STEP) {
         const int key = first_key + r;
         bool valid = key >= lo && key <= hi;
         size_t off = 0;
