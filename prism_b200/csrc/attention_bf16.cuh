@@ -190,13 +190,21 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         const __nv_bfloat16* Ks = KV + ((size_t)(warp * DEC_STAGES + it % DEC_STAGES) * 2) * SUB_ELEMS;
         const __nv_bfloat16* Vs = Ks + SUB_ELEMS;
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};     // odd k-steps: two shorter MMA chains
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            uint32_t b[4];
+        for (int ks = 0; ks < HD / 16; ks += 2) {
+            uint32_t b[4], b2[4];
             ldmatrix_x4(b, Ks + ((mat >> 1) * 8 + lr) * STRIDE + ks * 16 + (mat & 1) * 8);
+            ldmatrix_x4(b2, Ks + ((mat >> 1) * 8 + lr) * STRIDE + (ks + 1) * 16 + (mat & 1) * 8);
             mma_bf16_16816(s[0], qf[ks], b[0], b[1]);
             mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
+            mma_bf16_16816(s2[0], qf[ks + 1], b2[0], b2[1]);
+            mma_bf16_16816(s2[1], qf[ks + 1], b2[2], b2[3]);
         }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] += s2[nt][e];
         // mask (only a tile that crosses lo or hi needs it), scale, online softmax over this warp's
         // 16 keys (rows lane/4 and lane/4 + 8)
         const int key0 = tile * ATT_TILE + warp * 16 + (lane & 3) * 2;
@@ -232,10 +240,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
                           pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+        // the running maxima seldom move after the first tiles: rescale the output only when one did
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+        }
 #pragma unroll
         for (int j = 0; j < HD / 16; ++j) {
-            o[2 * j][0] *= corr[0]; o[2 * j][1] *= corr[0]; o[2 * j][2] *= corr[1]; o[2 * j][3] *= corr[1];
-            o[2 * j + 1][0] *= corr[0]; o[2 * j + 1][1] *= corr[0]; o[2 * j + 1][2] *= corr[1]; o[2 * j + 1][3] *= corr[1];
             uint32_t b[4];
             ldmatrix_x4_trans(b, Vs + ((mat & 1) * 8 + lr) * STRIDE + j * 16 + (mat >> 1) * 8);
             mma_bf16_16816(o[2 * j], pa, b[0], b[1]);

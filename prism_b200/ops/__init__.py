@@ -590,15 +590,17 @@ def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
 
 
 def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> int:
-    """How many CTAs share one (token, kv head)'s keys: enough to put two CTAs
-    on every SM, at most one per 64-key tile."""
+    """How many CTAs share one (token, kv head)'s keys: as many as fill one wave
+    of two CTAs per SM, at most one per 64-key tile.  More, shorter CTAs lose:
+    each pays the same fixed latencies (position, block table, first bytes, merge)."""
+    if os.environ.get("PRISM_DECODE_SPLITS"):
+        return int(os.environ["PRISM_DECODE_SPLITS"])
     span = min(max_kv_len, window + 64) if window else max_kv_len
     tiles = max(1, (span + 63) // 64)
-    fill = (2 * NUM_SMS) // max(1, T * nkv)          # one wave of two CTAs per SM, not a little more
-    balance = -(-tiles // 8)                          # at most ~8 tiles per CTA so that SMs finish together
-    n = max(1, min(tiles, 64, max(fill, balance)))
+    fill = (2 * NUM_SMS) // max(1, T * nkv)
+    n = max(1, min(tiles, 64, fill))
     if CLUSTER_MERGE and 8 < n <= 12:
-        n = 8                                         # one cluster of 8 beats a few more splits merged through memory
+        n = 8                                         # one cluster of 8 rather than a few more splits through memory
     return n
 
 
