@@ -215,7 +215,7 @@ def run(args):
     # pure decode step of the whole batch; tbt is the engine's own host clock between a request's tokens
     tbt = sum(r.tbt for r in res) / len(res)
     e2e = B / tbt if tbt > 0 else 0.0
-    lay_total = 4 * (3 * B + (B + 1) + 3 * B + B + B * (CONTEXT // PAGE) + 16)
+    lay_total = runner.last_h2d_bytes            # the packed batch descriptor of a decode step
 
     out = {
         "metric": "decode tok/s (Qwen2.5-7B shape, bf16, batch %d, 2048-token prompts)" % B,

@@ -57,6 +57,7 @@ class ModelRunner:
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]
         self._graphs: Dict[int, dict] = {}
         self.graph_kernel_launches = 0       # kernels of this library replayed inside graphs
+        self.last_h2d_bytes = 0              # bytes of the last step's batch descriptor (host to device)
 
     # ---- bookkeeping around a step -------------------------------------------
     def begin_request(self, req_id) -> None:
@@ -121,6 +122,7 @@ class ModelRunner:
             host = pack_batch(layout, tok, pos, seg_of, seg_start, cached, qlen, slots, rows,
                               block_rows, self.pad_page)
             dev = host.to(self.device, non_blocking=True)
+            self.last_h2d_bytes = host.numel() * 4
             ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions,
                               host_meta, max_q, max_kv)
             views = self.storage.views(ctx.block_tables, ctx.state_slots, slots)
@@ -180,6 +182,7 @@ class ModelRunner:
                           cached + [0] * pad, [1] * B, slots + [scratch_slot] * pad, list(range(B)),
                           br, self.pad_page)
         g["dev"].copy_(host, non_blocking=True)
+        self.last_h2d_bytes = host.numel() * 4
         g["graph"].replay()
         self.graph_kernel_launches += g["launches"]
         if not rows:

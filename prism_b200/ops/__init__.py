@@ -98,6 +98,9 @@ class _Sig:
     prism_argmax_split = [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_set_pdl = [_i]
     prism_gemm_tcgen05_supported = [_i, _i, _i]
+    prism_gemm_tcgen05_qkv_supported = [_i, _i, _i, _i, _i, _i]
+    prism_gemm_tcgen05_qkv = [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i,
+                              _i, _i, _p, _p]
     prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]
     prism_gemv_bf16_supported = [_i, _i, _i]
     prism_gemv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]
@@ -420,6 +423,37 @@ def rope_kv_write_partial(parts: torch.Tensor, bias: Optional[torch.Tensor], q_o
            "rope_kv_write_partial")
 
 
+QKV_FUSED = os.environ.get("PRISM_QKV_FUSED", "1") != "0"
+
+
+def gemm_tc_qkv(x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], q_out: torch.Tensor,
+                positions: torch.Tensor, tok_seg: torch.Tensor, table: Optional[torch.Tensor], rotary_dim: int,
+                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                block_table: Optional[torch.Tensor], num_pages: int, max_pos: int, nkv: int, ksplit: int,
+                err: torch.Tensor):
+    """The qkv projection of up to 16 tokens on the tensor-core GEMM with bias,
+    rotary encoding and the cache store in its epilogue: the K-splits of a
+    128-row tile form a thread-block cluster, exchange their partial sums through
+    distributed shared memory, and rank 0 writes q ``[T, nh, hd]`` and k, v."""
+    _cuda(x, qkv_w, qkv_b, q_out, positions, tok_seg, table, k_cache, v_cache, block_table)
+    M, K = x.shape
+    _, nh, hd = q_out.shape
+    assert qkv_w.shape == ((nh + 2 * nkv) * hd, K) and q_out.is_contiguous() and q_out.dtype == torch.bfloat16
+    assert x.dtype == torch.bfloat16 and qkv_w.dtype == torch.bfloat16 and x.stride(1) == 1 and qkv_w.stride(1) == 1
+    P = W = 0
+    if k_cache is not None:
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == torch.bfloat16
+        assert k_cache.shape[2:] == (nkv, hd)
+        P, W = k_cache.shape[1], block_table.shape[1]
+    if rotary_dim:
+        assert table.dtype == torch.float32 and table.shape == (M, rotary_dim // 2, 2)
+    _check(lib().prism_gemm_tcgen05_qkv(_ptr(qkv_w), qkv_w.stride(0), _ptr(x), x.stride(0) if M > 1 else K, _ptr(qkv_b),
+                                        F32 if qkv_b is None else _dt(qkv_b), M, K, int(ksplit), _ptr(q_out), nh * hd,
+                                        _ptr(positions), _ptr(tok_seg), _ptr(table), rotary_dim, _ptr(k_cache),
+                                        _ptr(v_cache), _ptr(block_table), W, P, num_pages, nh, nkv, hd, max_pos,
+                                        _ptr(err), _stream()), "gemm_tcgen05_qkv")
+
+
 def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], nh: int, nkv: int,
                      hd: int, rot, cache) -> torch.Tensor:
     """The front half of an attention layer: qkv projection (+ bias), rotary
@@ -437,6 +471,14 @@ def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[
             table = ctx.scratch[key] = ctx.alloc((T, rot.rotary_dim // 2, 2), torch.float32)
             rope_table(ctx.positions, rot.inv_freq, table)
     kc, vc = (cache.k, cache.v) if cache.write else (None, None)
+    rd = rot.rotary_dim if rot is not None else 0
+    if QKV_FUSED and tc_gemm_ok(x, qkv_w) and (rd == 0 or table is not None) and \
+            lib().prism_gemm_tcgen05_qkv_supported(T, x.shape[1], nh, nkv, hd, rd):
+        q = ctx.alloc((T, nh, hd), x.dtype)
+        ks = min(8, tc_ksplit(qkv_w.shape[0], qkv_w.shape[1]))
+        gemm_tc_qkv(x, qkv_w, qkv_b, q, ctx.positions, ctx.tok_seg, table, rd, kc, vc, cache.block_table,
+                    cache.num_pages, ctx.max_positions, nkv, ks, ctx.err)
+        return q
     if QKV_PARTIAL and table is not None and tc_gemm_ok(x, qkv_w) and hd % 8 == 0 and rot.rotary_dim % 16 == 0:
         ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
         if ks > 1:

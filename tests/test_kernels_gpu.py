@@ -352,6 +352,51 @@ def test_rope_kv_write_from_partial_sums(nh, nkv, hd, rd, P, dtype, with_bias):
         assert torch.allclose(vc[page, p_ % P].float(), tv[t], atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rd,P,K", [(28, 4, 128, 128, 256, 3584), (6, 2, 64, 64, 16, 136), (4, 2, 64, 32, 8, 200),
+                                              (2, 1, 128, 0, 16, 96)])
+@pytest.mark.parametrize("M", [1, 8, 16])
+@pytest.mark.parametrize("ksplit", [1, 2, 4])
+def test_fused_qkv_projection_rotary_store(nh, nkv, hd, rd, P, K, M, ksplit):
+    """The qkv GEMM with bias, rotary encoding and cache store in its epilogue
+    (cluster of K-splits) against: float32 product, float32 rotation, one rounding."""
+    ops = _ops()
+    D = (nh + 2 * nkv) * hd
+    x = _rand((M, K), torch.bfloat16, 60)
+    w = _rand((D, K), torch.bfloat16, 61, 0.05)
+    bias = _rand((D,), torch.bfloat16, 62)
+    W = 12
+    positions = torch.tensor([(37 * i + 5) % (W * P) for i in range(M)], dtype=torch.int32, device=DEV)
+    tok_seg = torch.arange(M, dtype=torch.int32, device=DEV)
+    pages = M * W
+    bt = torch.arange(pages, dtype=torch.int32, device=DEV).view(M, W)
+    table = None
+    inv = None
+    if rd:
+        inv = (1.0 / (1e4 ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))).to(DEV)
+        table = torch.empty(M, rd // 2, 2, dtype=torch.float32, device=DEV)
+        ops.rope_table(positions, inv, table)
+    kc = torch.zeros(pages, P, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = torch.full((M, nh, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = _err()
+    ops.gemm_tc_qkv(x, w, bias, q, positions, tok_seg, table, rd, kc, vc, bt, pages, 1 << 20, nkv, ksplit, err)
+    total = x.float() @ w.float().T + bias.float()
+    tq = total[:, :nh * hd].view(M, nh, hd)
+    tk = total[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd)
+    tv = total[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    rq = ref_rope(tq, positions, inv, rd) if rd else tq
+    rk = ref_rope(tk, positions, inv, rd) if rd else tk
+    scale = float(total.abs().max())
+    tol = dict(atol=1e-2 * scale, rtol=2e-2)
+    assert int(err) == 0 and torch.allclose(q.float(), rq, **tol)
+    for t in range(M):
+        p_ = int(positions[t])
+        page = int(bt[t, p_ // P])
+        assert torch.allclose(kc[page, p_ % P].float(), rk[t], **tol)
+        assert torch.allclose(vc[page, p_ % P].float(), tv[t], **tol)
+    assert int((kc != 0).any(dim=-1).any(dim=-1).sum()) <= M
+
+
 def test_sample_greedy_and_temperature():
     ops = _ops()
     R, V = 9, 152064 // 8 + 5
