@@ -1,0 +1,57 @@
+"""Layers of Qwen2.5-7B size (hidden 3584, 28/4 heads of 128, intermediate
+18944), two of them, with a reduced vocabulary so that the plain model can run
+on the CPU: the production kernels (tensor-core attention, the tcgen05 GEMM
+with its fused epilogues, the library GEMM for long portions) at the sizes
+they were written for, in float32 and bfloat16, whole and cut (GPU)."""
+
+import tempfile
+
+import pytest
+import torch
+
+from helpers import P, random_tokens, run_trace, trace_budget, trace_mixed, trace_tail, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=3584,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+                vocab_size=8192, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=32768, use_sliding_window=False)
+
+
+@pytest.fixture(scope="module")
+def folder_and_plain():
+    from prism_b200.weights.random_init import write_model_folder
+    with tempfile.TemporaryDirectory(prefix="prism_7b_shape_") as d:
+        write_model_folder(SHAPE_7B, 3, d)
+        cfg, t = P.load_folder(d)
+        seqs = {"a": random_tokens(8192, 150, 1), "b": random_tokens(8192, 41, 2), "c": random_tokens(8192, 77, 3)}
+        ref = {k: P.forward(cfg, t, v) for k, v in seqs.items()}
+        yield d, seqs, ref
+
+
+def runner_for(folder, dtype, num_pages, page_size=64):
+    from prism_b200.engine.runner import ModelRunner
+    from prism_b200.weights.loader import load_model_folder
+    tdt = getattr(torch, dtype)
+    _, model, pool = load_model_folder(folder, "cuda:0", tdt)
+    r = ModelRunner(model, "cuda:0", tdt, page_size, num_pages, 8)
+    r._pool = pool
+    return r
+
+
+@pytest.mark.parametrize("dtype,atol,rtol", [("float32", 1e-3, 1e-4), ("bfloat16", 5e-3, 4e-2)])
+@pytest.mark.parametrize("mode", ["whole", "tail", "mixed"])
+def test_7b_sized_layers(folder_and_plain, dtype, atol, rtol, mode):
+    folder, seqs, ref = folder_and_plain
+    steps = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 12), "mixed": lambda s: trace_mixed(s, seed=5)}[mode](seqs)
+    runner = runner_for(folder, dtype, trace_budget(steps, 64) // 64)
+    got = run_trace(runner, steps)
+    worst = 0.0
+    for rid, seq in seqs.items():
+        scale = float(ref[rid].abs().max())
+        for pos in range(len(seq)):
+            err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
+            worst = max(worst, err)
+            assert err <= atol + rtol * scale, (rid, pos, err, scale)
+    assert runner.cache.pages_in_use() == 0
