@@ -118,6 +118,7 @@ class CacheManager:
             num_pages = [num_pages] * len(self.groups)
         self.allocators: List[Optional[PageAllocator]] = [
             PageAllocator(n) if g.kind == "paged" else None for g, n in zip(self.groups, num_pages)]
+        self._paged = [g.index for g in self.groups if g.kind == "paged"]
         self._free_slots = list(range(self.max_seqs - 1, -1, -1))
         self.requests: Dict[object, RequestCache] = {}
         self.fresh_slots: List[int] = []        # slots handed out since the last drain (state to be cleared)
@@ -163,19 +164,22 @@ class CacheManager:
     def pages_needed(self, req_id, n_new: int) -> List[int]:
         """Pages each group must hand out before ``n_new`` more tokens can be written."""
         rc = self.requests[req_id]
-        total = self._pages_for(rc.length + n_new)
-        return [max(0, total - len(rc.pages[g.index])) if g.kind == "paged" else 0 for g in self.groups]
+        total = (rc.length + n_new + self.page_size - 1) // self.page_size
+        need = [0] * len(self.groups)
+        for gi in self._paged:
+            k = total - len(rc.pages[gi])
+            if k > 0:
+                need[gi] = k
+        return need
 
     def can_append(self, req_id, n_new: int, reserve: Optional[List[int]] = None) -> bool:
         """``reserve``: pages per group already promised to other requests of the same step."""
         if self.requests[req_id].length + n_new > self.max_seq_len:
             return False
         need = self.pages_needed(req_id, n_new)
-        for g, n in zip(self.groups, need):
-            if g.kind == "paged":
-                taken = reserve[g.index] if reserve else 0
-                if self.allocators[g.index].num_free - taken < n:
-                    return False
+        for gi in self._paged:
+            if need[gi] and self.allocators[gi].num_free - (reserve[gi] if reserve else 0) < need[gi]:
+                return False
         return True
 
     def append(self, req_id, n_new: int) -> None:
@@ -184,20 +188,26 @@ class CacheManager:
         rc = self.requests[req_id]
         if rc.length + n_new > self.max_seq_len:
             raise ValueError(f"request {req_id!r}: {rc.length + n_new} tokens exceed max_seq_len {self.max_seq_len}")
-        if not self.can_append(req_id, n_new):
-            raise OutOfPages(f"Out of KV cache pages for request {req_id!r} (+{n_new} tokens)")
-        for g, n in zip(self.groups, self.pages_needed(req_id, n_new)):
-            for _ in range(n):
-                rc.pages[g.index].append(self.allocators[g.index].alloc())
-        self.pages_high_water = max(self.pages_high_water, self.pages_in_use())
+        need = self.pages_needed(req_id, n_new)
+        for gi in self._paged:
+            if need[gi] > self.allocators[gi].num_free:
+                raise OutOfPages(f"Out of KV cache pages for request {req_id!r} (+{n_new} tokens)")
+        grew = False
+        for gi in self._paged:
+            for _ in range(need[gi]):
+                rc.pages[gi].append(self.allocators[gi].alloc())
+                grew = True
+        if grew:
+            self.pages_high_water = max(self.pages_high_water, self.pages_in_use())
 
     def commit(self, req_id, n_new: int) -> None:
         """The step has written ``n_new`` tokens: advance the length and give
         back the pages of windowed groups that no later query can see."""
         rc = self.requests[req_id]
         rc.length += n_new
-        assert all(self._pages_for(rc.length) <= len(rc.pages[g.index]) for g in self.groups if g.kind == "paged"), \
-            "commit beyond the pages appended"
+        total = (rc.length + self.page_size - 1) // self.page_size
+        for gi in self._paged:
+            assert total <= len(rc.pages[gi]), "commit beyond the pages appended"
         for g in self.groups:
             if g.kind != "paged" or g.need.window is None:
                 continue

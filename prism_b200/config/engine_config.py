@@ -31,6 +31,7 @@ class SchedulerConfig:
     max_batch_tokens: int = 4096        # tokens per step, decode tokens first
     max_num_seqs: int = 64              # requests running at once
     prefill_chunk: int = 2048           # most prompt tokens of one request per step
+    async_decode: bool = True           # launch the next decode step before reading the last one's tokens
 
 
 @dataclass

@@ -39,6 +39,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt_tokens + self.generated_tokens
 
+    def next_tokens(self, n: int) -> List[int]:
+        """The ``n`` tokens after the ``num_computed`` ones already in the cache."""
+        a, np_ = self.num_computed, len(self.prompt_tokens)
+        if a >= np_:
+            return self.generated_tokens[a - np_:a - np_ + n]
+        if a + n <= np_:
+            return self.prompt_tokens[a:a + n]
+        return self.prompt_tokens[a:] + self.generated_tokens[:a + n - np_]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt_tokens) + len(self.generated_tokens) - self.num_computed

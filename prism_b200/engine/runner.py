@@ -76,12 +76,14 @@ class ModelRunner:
         return True
 
     # ---- the step ----------------------------------------------------------------
-    @torch.no_grad()
-    def step(self, segments: Sequence[Segment]) -> Optional[torch.Tensor]:
+    def step(self, segments: Sequence[Segment], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the tokens of ``segments`` as one batch from the cache that
         earlier steps left; append them to the cache; return float32 logits
         ``[R, V]`` in the order of the segments and of their ``want`` lists
-        (None if nothing is wanted)."""
+        (None if nothing is wanted).  Nothing here waits for the GPU.
+        ``token_source`` (device int32, one token per segment, every segment a
+        single token): the token ids are taken from there on the device instead of
+        from ``segments`` - the previous step's sampled tokens, not yet read by the host."""
         if not segments:
             return None
         for s in segments:
@@ -116,13 +118,16 @@ class ModelRunner:
 
         S = len(segments)
         if self.use_cuda_graph and max_q == 1 and S <= self.graph_batch_sizes[-1]:
-            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows)
+            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows, token_source)
         else:
             layout = BatchLayout(len(tok), S, len(rows), self.cache.table_width, self.paged_groups)
             host = pack_batch(layout, tok, pos, seg_of, seg_start, cached, qlen, slots, rows,
                               block_rows, self.pad_page)
             dev = host.to(self.device, non_blocking=True)
             self.last_h2d_bytes = host.numel() * 4
+            if token_source is not None:
+                assert max_q == 1 and token_source.shape[0] >= S
+                layout.view(dev, "token_ids").copy_(token_source[:S], non_blocking=True)
             ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions,
                               host_meta, max_q, max_kv)
             views = self.storage.views(ctx.block_tables, ctx.state_slots, slots)
@@ -169,7 +174,7 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         return dict(graph=graph, layout=layout, dev=dev, out=out, launches=ops.launch_count - before)
 
-    def _step_graph(self, tok, pos, cached, slots, rows, block_rows):
+    def _step_graph(self, tok, pos, cached, slots, rows, block_rows, token_source=None):
         S = len(tok)
         B = self._bucket(S)
         g = self._graphs.get(B)
@@ -183,6 +188,8 @@ class ModelRunner:
                           br, self.pad_page)
         g["dev"].copy_(host, non_blocking=True)
         self.last_h2d_bytes = host.numel() * 4
+        if token_source is not None:
+            g["layout"].view(g["dev"], "token_ids")[:S].copy_(token_source[:S], non_blocking=True)
         g["graph"].replay()
         self.graph_kernel_launches += g["launches"]
         if not rows:

@@ -178,7 +178,7 @@ class Scheduler:
             return []
         segs, sampled = [], []
         for req, n in batch:
-            toks = req.tokens[req.num_computed:req.num_computed + n]
+            toks = req.next_tokens(n)
             last = req.num_computed + n == len(req.prompt_tokens) + len(req.generated_tokens)
             segs.append(Segment(req.id, toks, [n - 1] if last else []))
             if last:
@@ -222,6 +222,79 @@ class Scheduler:
             self.finished.append(req)
             self.stats.completed += 1
 
+    # ---- pipelined decoding ---------------------------------------------------------
+    def _steady(self) -> bool:
+        """Only decoding requests, nobody waiting: the next steps have the same
+        rows in the same order, so a step can be launched before the previous
+        step's tokens have been read."""
+        return (self.config.async_decode and hasattr(self.sampler, "sample_async") and not self.waiting
+                and bool(self.running) and len(self.running) <= self.config.max_batch_tokens
+                and all(r.remaining == 1 and r.generated_tokens for r in self.running))
+
+    def _pipelined_decode(self) -> bool:
+        """Decode the running set with one step always in flight: step i+1 takes its
+        token ids on the device from step i's sampler output, and the host reads
+        step i's tokens while step i+1 runs.  The pipeline drains when a request
+        finishes (its one extra token is dropped), when pages run out, or when a
+        request will reach its length limit; the ordinary ``step`` takes over.
+        Returns False if it could not launch anything."""
+        reqs = list(self.running)
+        seed_of = [r.params.seed if r.params.seed is not None else self.seed for r in reqs]
+        temps = [r.params.temperature for r in reqs]
+        n_launched = [len(r.generated_tokens) for r in reqs]       # tokens sampled or in flight, per request
+        inflight = []                                                  # sample handles, oldest first
+        source = None
+        stop = False
+        while True:
+            # launch the next step unless something ends the steady state
+            if not stop:
+                if any(n >= r.params.max_new_tokens for n, r in zip(n_launched, reqs)):
+                    stop = True
+                elif not all(self.cache.can_append(r.id, 1) for r in reqs) or not self.runner.can_run(
+                        [Segment(r.id, [0], [0]) for r in reqs]):
+                    stop = True
+            if not stop:
+                segs = [Segment(r.id, [r.generated_tokens[-1] if source is None else 0], [0]) for r in reqs]
+                logits = self.runner.step(segs, token_source=source)
+                us = [uniform(sd, r.id, n) for sd, r, n in zip(seed_of, reqs, n_launched)]
+                h = self.sampler.sample_async(logits, temps, us)
+                source = h.device_tokens
+                inflight.append(h)
+                for i in range(len(reqs)):
+                    n_launched[i] += 1
+                self.stats.steps += 1
+                self.stats.decode_tokens += len(reqs)
+            if not inflight:
+                return False
+            if len(inflight) < 2 and not stop:
+                continue                                               # keep one step ahead
+            tokens = self.sampler.read(inflight.pop(0))
+            now = time.time()
+            for req, tok in zip(reqs, tokens):
+                if req.state == RequestState.FINISHED:
+                    continue                                           # a token computed past its end: dropped
+                req.num_computed += 1
+                req.generated_tokens.append(int(tok))
+                self.stats.tokens_generated += 1
+                eos = req.params.eos_token_id if req.params.eos_token_id is not None else self.eos_token_id
+                if eos is not None and int(tok) == eos and not req.params.ignore_eos:
+                    req.finish_reason = "stop"
+                elif len(req.generated_tokens) >= req.params.max_new_tokens:
+                    req.finish_reason = "length"
+                if req.finish_reason:
+                    req.state, req.done_time = RequestState.FINISHED, now
+                    stop = True
+            if stop and not inflight:
+                break
+        for req in reqs:                                               # pages are given back once nothing in flight uses them
+            if req.state == RequestState.FINISHED:
+                self.runner.end_request(req.id)
+                self.running.remove(req)
+                self.finished.append(req)
+                self.stats.completed += 1
+        return True
+
     def run_to_completion(self) -> None:
         while self.has_work():
-            self.step()
+            if not (self._steady() and self._pipelined_decode()):
+                self.step()

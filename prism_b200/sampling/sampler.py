@@ -31,6 +31,13 @@ class SamplingParams:
     ignore_eos: bool = False
 
 
+@dataclass
+class SampleHandle:
+    event: object
+    host_tokens: torch.Tensor
+    device_tokens: torch.Tensor
+
+
 class Sampler:
     """One kernel launch per step for all rows; token ids come back through a
     pinned buffer."""
@@ -38,20 +45,34 @@ class Sampler:
     def __init__(self, device, max_rows: int = 256):
         self.device = torch.device(device)
         self.max_rows = max_rows
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
-        self._host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        # two sets of buffers: a step's tokens can still be read while the next step's are written
+        self._outs = [torch.empty(max_rows, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._hosts = [torch.empty(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], us: Sequence[float]) -> List[int]:
+        return self.read(self.sample_async(logits, temperatures, us))
+
+    def sample_async(self, logits: torch.Tensor, temperatures: Sequence[float], us: Sequence[float]):
+        """Launch the sampling kernel and the copy of the token ids to pinned host
+        memory without waiting.  Returns a handle for ``read``; ``handle.device_tokens``
+        (int32 ``[R]``) can feed the next step's token ids on the device."""
         R = logits.shape[0]
         if R > self.max_rows:
             self.__init__(self.device, max(R, 2 * self.max_rows))
-        out = self._out[:R]
+        self._turn ^= 1
+        out, host = self._outs[self._turn][:R], self._hosts[self._turn][:R]
         if any(t > 0 for t in temperatures):
             tu = torch.tensor([list(temperatures), list(us)], dtype=torch.float32, pin_memory=True)
             tu = tu.to(self.device, non_blocking=True)
             ops.sample(logits, tu[0], tu[1], out)
         else:
             ops.sample(logits, None, None, out)
-        self._host[:R].copy_(out, non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
-        return self._host[:R].tolist()
+        host.copy_(out, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        return SampleHandle(ev, host, out)
+
+    def read(self, handle) -> List[int]:
+        handle.event.synchronize()
+        return handle.host_tokens.tolist()
