@@ -555,3 +555,43 @@ def test_attention_finds_one_far_key(kind):
                                        None, scale, err)
         assert int(err) == 0
         assert torch.allclose(out[-1].float(), torch.full_like(out[-1].float(), 5.0), atol=0.05), (kind, far, out[-1][:4])
+
+
+@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill"])
+def test_attention_window_edge(kind):
+    """A sliding window's edge, made visible: the key just outside the window
+    carries an enormous score and a marked value and must not be seen; the key
+    just inside must be (move the mark there and it dominates)."""
+    ops = _ops()
+    nh, nkv, hd, P, window = 4, 2, 64, 16, 37
+    dtype = torch.float32 if kind == "generic32" else torch.bfloat16
+    for ctx in (36, 37, 64, 100, 129, 500):                        # the query sits at position ctx
+        segs = [(ctx, 1)] if kind != "prefill" else [(max(0, ctx - 5), ctx - max(0, ctx - 5) + 1)]
+        for inside in (False, True):
+            key = ctx - window + (1 if inside else 0)               # first key inside / last key outside
+            if key < 0:
+                continue
+            c = PagedCase(segs, nh, nkv, hd, P, dtype, seed=31)
+            c.q[-1] = 0
+            c.q[-1, :, 1] = 25.0
+            page, off = int(c.bt[0, key // P]), key % P
+            c.k[page, off, :, 1] = 25.0
+            c.v[page, off] = 7.0
+            out = torch.empty(c.T, nh * hd, dtype=dtype, device=DEV)
+            err = _err()
+            scale = hd ** -0.5
+            if kind.startswith("generic"):
+                ops.attention_generic(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, err)
+            elif kind == "decode":
+                ns = 3
+                ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, ns,
+                                          torch.empty(c.T, nh, ns, hd, device=DEV), torch.empty(c.T, nh, ns, 2, device=DEV), err)
+            else:
+                ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                                           window, scale, err)
+            last = out[-1].float()
+            assert int(err) == 0
+            if inside:
+                assert torch.allclose(last, torch.full_like(last, 7.0), atol=0.05), (kind, ctx, "inside key not found")
+            else:
+                assert float(last.abs().max()) < 3.0, (kind, ctx, "key outside the window was seen", float(last.abs().max()))
