@@ -301,6 +301,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (CLUSTER) {
             fin_o[r * HD + d] = acc;
             if (d == 0) { fin_m[r] = M; fin_l[r] = L; }
+        } else if (nsplit == 1) {
+            // the only split: this is the result, no partial and no merge
+            out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc * (1.f / L) : 0.f);
         } else {
             po[(size_t)r * nsplit * HD + d] = acc;
             if (d == 0) {
@@ -310,7 +313,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     }
     if (!CLUSTER) {
-        merge_if_last();
+        if (nsplit > 1) merge_if_last();
         return;
     }
     // every split's (max, sum, output) is in its CTA's shared memory: each CTA of the cluster merges
@@ -595,7 +598,7 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
     cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
                                    positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
                                    scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, counters, err);
-    if (rc != cudaSuccess || counters != nullptr) return (int)rc;
+    if (rc != cudaSuccess || counters != nullptr || nsplit == 1) return (int)rc;
     return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD >= 128 ? 128 : 64), 0, stream,
                               (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);
 }
