@@ -4,7 +4,7 @@ flushing L2 between timed launches, and prints achieved bandwidth or FLOP/s.
     python benchmarks/kernel_bench.py gemv  [--m 8]
     python benchmarks/kernel_bench.py gemm_tc [--m 8]
     python benchmarks/kernel_bench.py attn_decode [--batch 8 --ctx 4096]
-    python benchmarks/kernel_bench.py attn_prefill [--tokens 2048]
+    python benchmarks/kernel_bench.py attn_prefill [--tokens 2048] [--mma-sync]
     python benchmarks/kernel_bench.py small [--m 8]       (norm, rope, swiglu, embed, sample)
 
 With --once a case is launched a few times without timing (for ncu).
@@ -130,7 +130,8 @@ def bench_attn_prefill(args):
     cached.zero_()
     out = torch.empty(Tn, NH * HD, device=DEV, dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    fn = lambda: ops.attention_prefill_bf16(q, out, kc, vc, bt, seg_start, cached, Tn, n_pages, None, HD ** -0.5, err)
+    kern = ops.attention_prefill_bf16 if args.mma_sync else ops.attention_prefill_tc
+    fn = lambda: kern(q, out, kc, vc, bt, seg_start, cached, Tn, n_pages, None, HD ** -0.5, err)
     if args.once:
         for _ in range(3):
             fn()
@@ -138,7 +139,7 @@ def bench_attn_prefill(args):
         return
     t = timeit(fn)
     fl = 4 * NH * HD * (Tn * (Tn + 1) / 2)
-    print(f"attn_prefill T={Tn}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s (causal flops)")
+    print(f"attn_prefill ({'mma.sync' if args.mma_sync else 'tcgen05'}) T={Tn}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s (causal flops)")
 
 
 def bench_small(args):
@@ -175,6 +176,7 @@ if __name__ == "__main__":
     ap.add_argument("--bound", type=int, default=0, help="context bound used to choose the splits")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: CTAs per (token, kv head); 0 = the engine's choice")
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--mma-sync", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--once", action="store_true")
     a = ap.parse_args()
     {"gemv": bench_gemv, "gemm_tc": bench_gemm_tc, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill,

@@ -92,6 +92,9 @@ class _Sig:
                                    _p, _p, _i, _p, _i, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
+    prism_attention_prefill_tc_supported = [_i, _i, _i, _i]
+    prism_attention_prefill_tc = [_p, _i, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
+                                  _f, _p, _p]
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
@@ -627,6 +630,32 @@ def attention_prefill_bf16(q, out, k_cache, v_cache, block_table, seg_start, cac
                                               _stream()), "attention_prefill_bf16")
 
 
+def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seg_start, cached_len, max_q_len,
+                         num_pages, window, scale, err):
+    """The same on the 5th-generation tensor cores (tcgen05, TMA, tensor memory): 128 query
+    rows per CTA.  Head size 64 or 128, pages of a multiple of 64 tokens."""
+    _cuda(q, out, k_cache, v_cache, block_table, seg_start, cached_len)
+    T, nh, hd = q.shape
+    nkv, P = k_cache.shape[2], k_cache.shape[1]
+    S = cached_len.shape[0]
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1 and seg_start.shape[0] == S + 1
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+    _check(lib().prism_attention_prefill_tc(_ptr(q), q.stride(0), T, _ptr(out), out.stride(0), _ptr(k_cache),
+                                            _ptr(v_cache), k_cache.shape[0], _ptr(block_table), block_table.shape[1],
+                                            _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, hd,
+                                            P, num_pages, int(window or 0), float(scale), _ptr(err),
+                                            _stream()), "attention_prefill_tc")
+
+
+def attention_prefill_tc_supported(hd: int, nh: int, nkv: int, page_size: int) -> bool:
+    return bool(lib().prism_attention_prefill_tc_supported(hd, nh, nkv, page_size))
+
+
+ATTENTION_TC = os.environ.get("PRISM_ATTN_TC", "1") != "0"
+ATTENTION_TC_MIN_Q = int(os.environ.get("PRISM_ATTN_TC_MIN_Q", "64"))     # shorter portions: 64-row mma.sync tiles
+
+
 def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
     return bool(lib().prism_attention_bf16_supported(hd, nh, nkv))
 
@@ -659,6 +688,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
             part_ml = ctx.alloc((T, nh, nsplit, 2), torch.float32)
             attention_decode_bf16(q, out, cache.k, cache.v, cache.block_table, ctx.positions, ctx.tok_seg,
                                   cache.num_pages, window, scale, nsplit, part_o, part_ml, ctx.err)
+        elif (ATTENTION_TC and ctx.max_q_len >= ATTENTION_TC_MIN_Q and scale > 0 and cache.k.is_contiguous()
+              and cache.v.is_contiguous() and attention_prefill_tc_supported(hd, nh, nkv, cache.k.shape[1])):
+            attention_prefill_tc(q, out, cache.k, cache.v, cache.block_table, ctx.seg_start, ctx.cached_len,
+                                 ctx.max_q_len, cache.num_pages, window, scale, ctx.err)
         else:
             attention_prefill_bf16(q, out, cache.k, cache.v, cache.block_table, ctx.seg_start, ctx.cached_len,
                                    ctx.max_q_len, cache.num_pages, window, scale, ctx.err)

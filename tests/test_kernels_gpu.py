@@ -524,16 +524,56 @@ def test_attention_prefill_bf16(case):
     assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
-@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill"])
+PREFILL_TC_CASES = [
+    (28, 4, 128, 256, None, [(0, 200), (300, 1), (64, 64), (5, 63), (0, 1), (1000, 65)]),
+    (8, 8, 64, 64, None, [(0, 130), (17, 2)]),
+    (16, 1, 64, 64, 50, [(0, 180), (49, 3), (50, 1), (400, 70)]),
+    (14, 2, 128, 128, 64, [(100, 129), (0, 64)]),
+    (4, 2, 128, 64, None, [(0, 700)]),
+    (6, 2, 128, 192, None, [(130, 300), (0, 127), (0, 128), (63, 129)]),
+    (3, 1, 64, 64, 200, [(0, 517)]),
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_TC_CASES)
+def test_attention_prefill_tc(case):
+    """The tcgen05 kernel: 128-row query tiles, keys by TMA through the block table."""
+    ops = _ops()
+    nh, nkv, hd, P, window, segs = case
+    c = PagedCase(segs, nh, nkv, hd, P, torch.bfloat16, seed=24)
+    out = torch.full((c.T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = _err()
+    scale = hd ** -0.5
+    assert ops.attention_prefill_tc_supported(hd, nh, nkv, P)
+    ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
+    for _ in range(2):
+        out.fill_(float("nan"))
+        ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                                 window, scale, err)
+        assert int(err) == 0 and not torch.isnan(out.float()).any()
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+
+
+def test_attention_prefill_tc_refuses():
+    ops = _ops()
+    assert not ops.attention_prefill_tc_supported(48, 4, 2, 64)
+    assert not ops.attention_prefill_tc_supported(128, 4, 2, 16)
+    c = PagedCase([(0, 20)], 4, 2, 128, 16, torch.bfloat16, seed=1)
+    with pytest.raises(ops.KernelError):
+        ops.attention_prefill_tc(c.q, torch.empty(c.T, 4 * 128, dtype=torch.bfloat16, device=DEV), c.k, c.v, c.bt,
+                                 c.seg_start, c.cached_len, c.max_q, c.num_pages, None, 1.0, _err())
+
+
+@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill", "prefill_tc"])
 def test_attention_finds_one_far_key(kind):
     """One key among thousands carries the whole softmax: the query and that
     key are scaled so that its score stands out, and its value is marked.  A
     kernel that drops a tile, a split or a page loses the mark."""
     ops = _ops()
-    nh, nkv, hd, P = 8, 2, 64, 16
+    nh, nkv, hd, P = 8, 2, 64, (64 if kind == "prefill_tc" else 16)
     dtype = torch.float32 if kind == "generic32" else torch.bfloat16
     ctx = 3000
-    segs = [(ctx, 1)] if kind != "prefill" else [(ctx - 40, 41)]
+    segs = [(ctx, 1)] if not kind.startswith("prefill") else [(ctx - 40, 41)]
     for far in (0, 17, 1234, 2047, 2048, ctx - 1, ctx):
         c = PagedCase(segs, nh, nkv, hd, P, dtype, seed=23)
         c.q[:] = 0
@@ -550,6 +590,9 @@ def test_attention_finds_one_far_key(kind):
             ns = 9
             ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, None, scale, ns,
                                       torch.empty(c.T, nh, ns, hd, device=DEV), torch.empty(c.T, nh, ns, 2, device=DEV), err)
+        elif kind == "prefill_tc":
+            ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                                     None, scale, err)
         else:
             ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
                                        None, scale, err)
@@ -557,16 +600,16 @@ def test_attention_finds_one_far_key(kind):
         assert torch.allclose(out[-1].float(), torch.full_like(out[-1].float(), 5.0), atol=0.05), (kind, far, out[-1][:4])
 
 
-@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill"])
+@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill", "prefill_tc"])
 def test_attention_window_edge(kind):
     """A sliding window's edge, made visible: the key just outside the window
     carries an enormous score and a marked value and must not be seen; the key
     just inside must be (move the mark there and it dominates)."""
     ops = _ops()
-    nh, nkv, hd, P, window = 4, 2, 64, 16, 37
+    nh, nkv, hd, P, window = 4, 2, 64, (64 if kind == "prefill_tc" else 16), 37
     dtype = torch.float32 if kind == "generic32" else torch.bfloat16
     for ctx in (36, 37, 64, 100, 129, 500):                        # the query sits at position ctx
-        segs = [(ctx, 1)] if kind != "prefill" else [(max(0, ctx - 5), ctx - max(0, ctx - 5) + 1)]
+        segs = [(ctx, 1)] if not kind.startswith("prefill") else [(max(0, ctx - 5), ctx - max(0, ctx - 5) + 1)]
         for inside in (False, True):
             key = ctx - window + (1 if inside else 0)               # first key inside / last key outside
             if key < 0:
@@ -586,6 +629,9 @@ def test_attention_window_edge(kind):
                 ns = 3
                 ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, ns,
                                           torch.empty(c.T, nh, ns, hd, device=DEV), torch.empty(c.T, nh, ns, 2, device=DEV), err)
+            elif kind == "prefill_tc":
+                ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                                         window, scale, err)
             else:
                 ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
                                            window, scale, err)
