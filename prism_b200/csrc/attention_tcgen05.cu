@@ -35,6 +35,7 @@ constexpr int BQ = 128;              // query rows per CTA (UMMA M)
 constexpr int BK = 64;               // keys per tile
 constexpr int THREADS = 192;
 constexpr int STAGES = 2;
+constexpr float RESCALE_STEP = 8.f;  // log2 units
 
 template <int HD> struct ACfg {
     static constexpr int HALVES = HD / 64;                       // 64-column (128-byte) boxes per row
@@ -113,10 +114,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     using C = ACfg<HD>;
     pdl_trigger();
     pdl_wait();
-    const int seg = blockIdx.z, h = blockIdx.y;
+    // Heads vary fastest, and later query tiles (which see more keys) come first: the longest CTAs of
+    // all heads start together and the short ones fill the gaps; the heads of one kv group walk the
+    // same keys at the same time, so K and V are read from HBM once.
+    const int seg = blockIdx.z, h = blockIdx.x;
     const int s0 = seg_start[seg], qlen = seg_start[seg + 1] - s0;
-    // later query tiles see more keys: they are started first
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * BQ;
+    const int q0 = (gridDim.y - 1 - blockIdx.y) * BQ;
     if (q0 >= qlen) return;
 
     extern __shared__ unsigned char smem_raw[];
@@ -276,9 +279,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
 #pragma unroll
             for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
-            const float m_new = fmaxf(m_run, mx * scale_log2);         // scale_log2 > 0
+            // The exponent's reference m_run follows the row maximum lazily: it moves only when the
+            // maximum has grown by more than 2^RESCALE_STEP, so that O seldom has to be rescaled.  Until
+            // then the probabilities are at most 2^RESCALE_STEP instead of 1, which float32 sums and bf16
+            // operands hold just as well; the final division by the sum (same reference) makes it exact.
+            const float m_tile = mx * scale_log2;                      // scale_log2 > 0
+            const bool move = m_tile - m_run > RESCALE_STEP;           // also the first visible key (m_run = -inf)
+            const float m_new = move ? m_tile : m_run;
             const float mu = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = ex2(m_run - mu);                        // 0 for a row that saw nothing yet
+            const float corr = move ? ex2(m_run - mu) : 1.f;           // 0 for a row that saw nothing yet
             float lsum = 0.f;
             uint32_t pr[32];
 #pragma unroll
@@ -375,7 +384,7 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
     if (rc) return rc;
     auto kern = attn_prefill_tc_kernel<HD>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
-    dim3 grid((max_q_len + BQ - 1) / BQ, nh, S);
+    dim3 grid(nh, (max_q_len + BQ - 1) / BQ, S);
     return (int)launch_kernel(kern, grid, dim3(THREADS), C::SMEM, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride, bt,
                               bt_width, seg_start, cached_len, nh, nkv, page_size, num_pages, window,
                               scale * 1.4426950408889634f, err);
@@ -397,7 +406,7 @@ PRISM_EXPORT int prism_attention_prefill_tc(const void* q, int q_stride, int T, 
                                             int nkv, int hd, int page_size, int num_pages, int window, float scale,
                                             int* err, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0 || T <= 0) return 0;
-    if (!prism_attention_prefill_tc_supported(hd, nh, nkv, page_size) || S > 65535 || nh > 65535 || q_stride % 8 ||
+    if (!prism_attention_prefill_tc_supported(hd, nh, nkv, page_size) || S > 65535 || (max_q_len + prism::tca::BQ - 1) / prism::tca::BQ > 65535 || q_stride % 8 ||
         out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
         num_pages > cache_pages || scale <= 0.f)
         return (int)cudaErrorInvalidValue;
