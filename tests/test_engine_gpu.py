@@ -124,6 +124,28 @@ def test_decode_many_requests_with_graphs_and_padding_rows():
         assert r.token_ids == P.generate(cfg, t, p, s.max_new_tokens)
 
 
+@pytest.mark.parametrize("name", ["D", "B"])
+def test_decoding_requests_beside_a_prompt_portion(name, monkeypatch):
+    """Five requests are decoding when a long prompt arrives and is prefilled in portions beside them:
+    in those steps the single tokens go through the decode attention kernel and the portion through
+    the prefill kernel.  Everybody's tokens are the plain model's."""
+    from prism_b200 import SamplingParams, ops
+    monkeypatch.setattr(ops, "MIXED_SPLIT_MIN", 2)          # the product splits from 12 decoding requests on
+    vocab = TINY[name][0]["vocab_size"]
+    eng = engine(name, "bfloat16", prefill_chunk=80, max_batch_tokens=96, page_size=64, num_pages=40)
+    short = [random_tokens(vocab, n, 300 + n) for n in (3, 9, 14, 6, 11)]
+    reqs = [eng.scheduler.add_request(p, SamplingParams(max_new_tokens=14)) for p in short]
+    for _ in range(3):
+        eng.scheduler.step()
+    long_prompt = random_tokens(vocab, 230, 77)
+    reqs.append(eng.scheduler.add_request(long_prompt, SamplingParams(max_new_tokens=5)))
+    eng.scheduler.run_to_completion()
+    eng.runner.check_errors()
+    for p, r in zip(short + [long_prompt], reqs):
+        assert len(r.generated_tokens) == r.params.max_new_tokens
+        near_greedy(name, p, r.generated_tokens, 0.03)
+
+
 def test_bad_token_id_is_reported_not_faulted():
     from prism_b200 import SamplingParams
     from prism_b200.engine.runner import DeviceError
