@@ -46,3 +46,22 @@ def test_cutting(name, dtype, mode):
     assert len(got) == sum(len(s) for s in seqs.values())
     compare_with_plain(name, seqs, got, **TOL[dtype])
     assert runner.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cutting_with_64_token_pages(mode, monkeypatch):
+    """Head size 64 with pages of 64 tokens: portions of 64 tokens and more run on the
+    tcgen05 attention kernel, shorter ones on the mma.sync kernel, and in mixed steps the
+    decoding requests at the head of the batch go to the decode kernel."""
+    from prism_b200 import ops
+    monkeypatch.setattr(ops, "MIXED_SPLIT_MIN", 2)
+    name, dtype, ps = "D", "bfloat16", 64
+    seqs = sequences(name)
+    steps = {"whole": trace_whole, "tail": trace_tail, "portions": trace_portions,
+             "mixed": lambda s: trace_mixed(s, seed=11)}[mode](seqs)
+    budget = trace_budget(steps, ps)
+    runner = make_runner(name, dtype, num_pages=budget // ps, page_size=ps)
+    got = run_trace(runner, steps)
+    assert len(got) == sum(len(s) for s in seqs.values())
+    compare_with_plain(name, seqs, got, **TOL[dtype])
+    assert runner.cache.pages_in_use() == 0
