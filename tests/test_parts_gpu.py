@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation's function of the same
-name, and a toy mixer with state of its own - defined here, registered, built
-and stepped without touching the framework's files (GPU)."""
+name, and toy parts - a mixer with state of its own, a position encoding with
+weights, a feed-forward with routing - defined here, registered, built and
+stepped without touching the framework's files (GPU)."""
 
 import tempfile
 
@@ -274,3 +275,148 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
                 for pos in range(len(seq)):
                     err = float((got[(rid, pos)] - ref[pos]).abs().max())
                     assert err < 5e-5, (rid, pos, err)
+
+
+# --------------------------------------------------------------------------
+# a second toy architecture: a position encoding with weights of its own (a learned
+# table added to q and k) and a feed-forward with routing (top-1 of small experts,
+# router logits in float32), beside the stock parts; different mixers' settings and
+# feed-forwards in different layers
+# --------------------------------------------------------------------------
+
+N_EXPERTS, EXPERT_WIDTH, MAX_POS = 3, 24, 160
+
+
+def register_toy_routed():
+    from prism_b200.model_registry import register_architecture
+    from prism_b200.models.decoder import ModelSpec
+    from prism_b200.parts import FeedForward, ParamSpec, PartSpec, PositionEncoding, WeightSource, register_part
+
+    @register_part("position", "toy_learned")
+    class ToyLearnedPositions(PositionEncoding):
+        """q[t, h] += table[pos_t]; k[t, h] += table[pos_t].  Not a rotary encoding: the mixer
+        calls ``apply``."""
+
+        def __init__(self, head_dim, max_positions):
+            self.hd, self.n = head_dim, max_positions
+
+        def params(self):
+            return [ParamSpec("table", (WeightSource("table", (self.n, self.hd)),))]
+
+        def apply(self, ctx, q, k):
+            add = self.w["table"][ctx.positions.long()].to(q.dtype)[:, None, :]
+            q += add
+            k += add
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class ToyTop1Experts(FeedForward):
+        """Each token goes to the expert whose router logit (float32) is largest; its output is
+        scaled by that expert's softmax probability."""
+
+        def __init__(self, hidden_size, experts, expert_width):
+            self.h, self.e, self.w_ = hidden_size, experts, expert_width
+
+        def params(self):
+            ps = [ParamSpec("router", (WeightSource("router.weight", (self.e, self.h)),))]
+            for i in range(self.e):
+                ps.append(ParamSpec(f"up{i}", (WeightSource(f"experts.{i}.up.weight", (self.w_, self.h)),)))
+                ps.append(ParamSpec(f"down{i}", (WeightSource(f"experts.{i}.down.weight", (self.h, self.w_)),)))
+            return ps
+
+        def forward(self, ctx, x):
+            logits = x.float() @ self.w["router"].float().T
+            prob = torch.softmax(logits, -1)
+            pick = logits.argmax(-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for i in range(self.e):
+                rows = (pick == i).nonzero().flatten()
+                if rows.numel():
+                    h = torch.nn.functional.silu(x[rows].float() @ self.w[f"up{i}"].float().T)
+                    out[rows] = (h @ self.w[f"down{i}"].float().T) * prob[rows, i:i + 1]
+            return out.to(x.dtype)
+
+    def spec(cfg):
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        norm = lambda p, eps: PartSpec("rmsnorm", dict(width=H, eps=eps), prefix=p)
+        l0 = PartSpec("prenorm", dict(
+            mixer=PartSpec("gqa_attention", dict(hidden_size=H, num_heads=3, num_kv_heads=1, head_dim=16, qkv_bias=True,
+                                                 position=PartSpec("toy_learned", dict(head_dim=16, max_positions=MAX_POS),
+                                                                   prefix="l0.attn.pos.")),
+                           prefix="l0.attn."),
+            feed_forward=PartSpec("toy_top1_experts", dict(hidden_size=H, experts=N_EXPERTS, expert_width=EXPERT_WIDTH),
+                                  prefix="l0.moe."),
+            mixer_norm=norm("l0.n1.", 1e-5), ff_norm=norm("l0.n2.", 1e-5)))
+        l1 = PartSpec("prenorm", dict(
+            mixer=PartSpec("gqa_attention", dict(hidden_size=H, num_heads=2, num_kv_heads=2, head_dim=32, qkv_bias=False,
+                                                 window=19, position=PartSpec("rotary", dict(head_dim=32, theta=5e3, rotary_dim=16))),
+                           prefix="l1.attn."),
+            feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=cfg["intermediate_size"]), prefix="l1.ff."),
+            mixer_norm=norm("l1.n1.", 1e-6), ff_norm=norm("l1.n2.", 1e-6)))
+        return ModelSpec("ToyRoutedForCausalLM", H, V, MAX_POS,
+                         PartSpec("token", dict(vocab_size=V, hidden_size=H), prefix="emb."), [l0, l1],
+                         norm("final.", 1e-6), PartSpec("linear", dict(vocab_size=V, hidden_size=H), prefix="head."))
+
+    register_architecture("ToyRoutedForCausalLM", lambda raw: raw, spec)
+
+
+def toy_routed_plain(t, tokens):
+    T = len(tokens)
+    x = t["emb.embed_tokens.weight"][torch.tensor(tokens)]
+    # layer 0: learned positions, one kv head, routed feed-forward
+    h = P.rms_norm(x, t["l0.n1.weight"], 1e-5)
+    add = t["l0.attn.pos.table"][:T][:, None, :]
+    q = (h @ t["l0.attn.q_proj.weight"].T + t["l0.attn.q_proj.bias"]).view(T, 3, 16) + add
+    k = (h @ t["l0.attn.k_proj.weight"].T + t["l0.attn.k_proj.bias"]).view(T, 1, 16) + add
+    v = (h @ t["l0.attn.v_proj.weight"].T + t["l0.attn.v_proj.bias"]).view(T, 1, 16)
+    x = x + P.attention(q, k, v).reshape(T, 48) @ t["l0.attn.o_proj.weight"].T
+    h = P.rms_norm(x, t["l0.n2.weight"], 1e-5)
+    logits = h @ t["l0.moe.router.weight"].T
+    prob, pick = torch.softmax(logits, -1), logits.argmax(-1)
+    out = torch.zeros_like(h)
+    for i in range(T):
+        e = int(pick[i])
+        out[i] = (torch.nn.functional.silu(h[i] @ t[f"l0.moe.experts.{e}.up.weight"].T)
+                  @ t[f"l0.moe.experts.{e}.down.weight"].T) * prob[i, e]
+    x = x + out
+    # layer 1: partial rotary (16 of 32), window 19, dense feed-forward
+    h = P.rms_norm(x, t["l1.n1.weight"], 1e-6)
+    cos, sin = P.rope_cos_sin(torch.arange(T), 16, 5e3)
+    q = (h @ t["l1.attn.q_proj.weight"].T).view(T, 2, 32).clone()
+    k = (h @ t["l1.attn.k_proj.weight"].T).view(T, 2, 32).clone()
+    q[..., :16], k[..., :16] = P.apply_rope(q[..., :16], cos, sin), P.apply_rope(k[..., :16], cos, sin)
+    v = (h @ t["l1.attn.v_proj.weight"].T).view(T, 2, 32)
+    x = x + P.attention(q, k, v, 19).reshape(T, 64) @ t["l1.attn.o_proj.weight"].T
+    h = P.rms_norm(x, t["l1.n2.weight"], 1e-6)
+    x = x + P.swiglu(h @ t["l1.ff.gate_proj.weight"].T, h @ t["l1.ff.up_proj.weight"].T) @ t["l1.ff.down_proj.weight"].T
+    return P.rms_norm(x, t["final.weight"], 1e-6) @ t["head.weight"].T
+
+
+def test_toy_position_encoding_and_routed_feed_forward():
+    """Another position encoding (with weights of its own) and a feed-forward with routing,
+    defined here and registered, make a model with the stock attention: built from a
+    configuration, written and loaded by tensor name, stepped whole, in portions and mixed."""
+    from safetensors.torch import load_file
+    from prism_b200.engine.runner import ModelRunner
+    from prism_b200.weights.loader import load_model_folder
+    from prism_b200.weights.random_init import write_model_folder
+    from helpers import run_trace, trace_mixed, trace_portions, trace_whole, trace_budget
+    register_toy_routed()
+    raw = dict(architectures=["ToyRoutedForCausalLM"], hidden_size=40, intermediate_size=56, vocab_size=83)
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(raw, 5, d, store_dtype=torch.float32)
+        t = load_file(d + "/model.safetensors")
+        assert t["l0.attn.pos.table"].shape == (MAX_POS, 16) and t["l0.moe.experts.2.down.weight"].shape == (40, EXPERT_WIDTH)
+        seqs = {f"r{i}": random_tokens(83, n, 60 + i) for i, n in enumerate([4, 27, 50, 90])}
+        for make in (trace_whole, trace_portions, lambda s: trace_mixed(s, seed=9)):
+            steps = make(seqs)
+            _, model, pool = load_model_folder(d, DEV, torch.float32)
+            assert [n.window for n in model.cache_needs()] == [None, 19]
+            runner = ModelRunner(model, DEV, torch.float32, 8, trace_budget(steps, 8) // 8, 4)
+            assert len(runner.groups) == 2                        # all keys / a window of them
+            got = run_trace(runner, steps)
+            for rid, seq in seqs.items():
+                ref = toy_routed_plain(t, seq)
+                for pos in range(len(seq)):
+                    err = float((got[(rid, pos)] - ref[pos]).abs().max())
+                    assert err < 5e-5, (rid, pos, err)
+            assert runner.cache.pages_in_use() == 0
