@@ -207,7 +207,7 @@ def run(args):
         points[f"decode_b{b}"] = round(b / m * 1e3, 1)
 
     # ---- end to end through Engine.generate: host token ids in, host token ids out ----
-    n_new = max(8, min(K, 64))
+    n_new = max(8, min(K, 256))      # the first ~20 steps after the prompts run at the lower clocks the prefill left
     res = eng.generate(prompts(B), SamplingParams(max_new_tokens=n_new, ignore_eos=True))   # warm
     t_first = time.perf_counter()
     res = eng.generate(prompts(B), SamplingParams(max_new_tokens=n_new, ignore_eos=True))
