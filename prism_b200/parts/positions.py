@@ -11,6 +11,9 @@ import torch
 from .base import PositionEncoding, RotaryParams, register_part
 
 
+_INV_FREQ = {}      # (device, theta, rotary_dim) -> float32 inverse frequencies on that device
+
+
 @register_part("position", "rotary")
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, head_dim: int, theta: float, rotary_dim: int = None):
@@ -24,8 +27,14 @@ class RotaryEmbedding(PositionEncoding):
     def on_bound(self):
         rd = self.rotary_dim
         # the formula of executor.py:50, evaluated in float32 on the host
-        inv = 1.0 / (self.theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))
-        self._params = RotaryParams(inv.to(self.device), rd)
+        # layers with the same constants share one device table, so the per-step cos/sin table that
+        # the kernels build from it is built once per step, not once per layer
+        key = (str(self.device), self.theta, rd)
+        inv = _INV_FREQ.get(key)
+        if inv is None:
+            inv = (1.0 / (self.theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))).to(self.device)
+            _INV_FREQ[key] = inv
+        self._params = RotaryParams(inv, rd)
 
     def rotary(self):
         return self._params
