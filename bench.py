@@ -109,7 +109,7 @@ def run(args):
     pages_per_seq = CONTEXT // PAGE
     ec = EngineConfig(kv_page_size=PAGE, num_pages=64 * pages_per_seq + 8, max_seq_len=CONTEXT, use_cuda_graph=True,
                       graph_batch_sizes=(1, 8, 64),
-                      scheduler=SchedulerConfig(max_batch_tokens=8 * PROMPT, max_num_seqs=64, prefill_chunk=PROMPT))
+                      scheduler=SchedulerConfig(max_batch_tokens=max(8, B) * PROMPT, max_num_seqs=64, prefill_chunk=PROMPT))
     eng = Engine(None, ec, dtype="bfloat16", config=cfg, random_seed=0)
     runner, dev = eng.runner, eng.device
     g = torch.Generator().manual_seed(1)
