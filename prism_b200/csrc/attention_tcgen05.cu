@@ -135,8 +135,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* v_empty = bars + 7;     // [2]
     uint64_t* s_full = bars + 9;      // [2]
     uint64_t* p_full = bars + 11;     // [2]
-    uint64_t* pv_done = bars + 13;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* pv_done = bars + 13;    // a phase per P V product: O may be rescaled
+    uint64_t* o_done = bars + 14;     // one phase: the last P V product is complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,6 +159,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 128);
         }
         mbar_init(pv_done, 1);
+        mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -244,6 +246,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                     umma_commit(&v_empty[s]);
                     umma_commit(pv_done);
+                    if (jj == n - 1) umma_commit(o_done);
                 }
             }
         }
@@ -337,7 +340,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(&p_full[s]);
         }
         pdl_trigger_gemm();
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (n - 1) & 1, abortp));
+        // Not pv_done: its phases are told apart by one parity bit, and here the product before the last
+        // may still be running (it was issued after the S that this warp just finished with), so a wait
+        // for the last phase's parity could pass two phases early.  Inside the loop a waiter is never more
+        // than one phase behind: the product two tiles back was issued before the S it has just read.
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0, abortp));
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

@@ -55,3 +55,29 @@ def test_7b_sized_layers(folder_and_plain, dtype, atol, rtol, mode):
             worst = max(worst, err)
             assert err <= atol + rtol * scale, (rid, pos, err, scale)
     assert runner.cache.pages_in_use() == 0
+
+
+def test_a_step_gives_the_same_bits_every_time():
+    """The same prompt, prefilled again and again from recycled pages, gives bitwise the same
+    logits.  A race shows here as a rare different result: a wait on a barrier whose phases are told
+    apart by one parity bit once passed two phases early in the tcgen05 attention kernel when the
+    neighbouring CTA kept the tensor pipe busy - about one step in ten, with four full-size layers and
+    the full vocabulary (random weights made on the device; no plain model is needed for this)."""
+    from prism_b200 import Engine, EngineConfig
+    from prism_b200.engine.batch import Segment
+    cfg = dict(SHAPE_7B, num_hidden_layers=4, vocab_size=152064)
+    eng = Engine(None, EngineConfig(kv_page_size=64, num_pages=300, max_seq_len=4096, use_cuda_graph=False),
+                 dtype="bfloat16", config=cfg, random_seed=0)
+    runner = eng.runner
+    prompt = random_tokens(150000, 200, 9)
+
+    def once():
+        runner.begin_request("r")
+        a = runner.step([Segment("r", prompt, [199])]).clone()
+        runner.end_request("r")
+        return a
+
+    ref = once()
+    differ = [i for i in range(80) if not torch.equal(once(), ref)]
+    runner.check_errors()
+    assert not differ, differ

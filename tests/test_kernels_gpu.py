@@ -554,6 +554,32 @@ def test_attention_prefill_tc(case):
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
+def test_attention_prefill_tc_is_reproducible():
+    """The same call gives the same bits every time.  (A wait on a barrier whose phases are told
+    apart by one parity bit once passed two phases early when the tensor pipe was busy with the
+    neighbouring CTA; it showed as a different result every twentieth call or so.)"""
+    ops = _ops()
+    nh, nkv, hd, P = 28, 4, 128, 256
+    c = PagedCase([(0, 1100)], nh, nkv, hd, P, torch.bfloat16, seed=25)
+    err = _err()
+    outs = []
+    res = torch.zeros(c.T, 3584, device=DEV)
+    w = torch.ones(3584, dtype=torch.bfloat16, device=DEV)
+    normed = torch.empty(c.T, 3584, dtype=torch.bfloat16, device=DEV)
+    for _ in range(120):
+        out = torch.empty((c.T, nh * hd), dtype=torch.bfloat16, device=DEV)
+        # a short kernel before it, as in a layer: the attention CTAs become resident while it runs
+        # (programmatic dependent launch) and are released together
+        ops.add_rmsnorm(res, None, w, 1e-6, normed)
+        ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
+                                 None, hd ** -0.5, err)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert int(err) == 0
+    differ = [i for i, o in enumerate(outs) if not torch.equal(o, outs[0])]
+    assert not differ, differ
+
+
 def test_attention_prefill_tc_refuses():
     ops = _ops()
     assert not ops.attention_prefill_tc_supported(48, 4, 2, 64)
