@@ -65,3 +65,15 @@ def test_cutting_with_64_token_pages(mode, monkeypatch):
     assert len(got) == sum(len(s) for s in seqs.values())
     compare_with_plain(name, seqs, got, **TOL[dtype])
     assert runner.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("name,dtype,ps", [("D", "bfloat16", 64), ("C", "bfloat16", 16), ("B", "float32", 8)])
+def test_replay_is_reproducible(name, dtype, ps):
+    """The same trace on the same runner (pages recycled in between) gives bitwise the same logits."""
+    seqs = sequences(name)
+    steps = trace_mixed(seqs, seed=13)
+    runner = make_runner(name, dtype, num_pages=trace_budget(steps, ps) // ps, page_size=ps)
+    ref = run_trace(runner, steps)
+    for _ in range(3):
+        got = run_trace(runner, steps)
+        assert all(torch.equal(got[k], ref[k]) for k in ref)
