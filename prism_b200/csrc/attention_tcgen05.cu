@@ -135,9 +135,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* v_empty = bars + 7;     // [2]
     uint64_t* s_full = bars + 9;      // [2]
     uint64_t* p_full = bars + 11;     // [2]
-    uint64_t* pv_done = bars + 13;    // a phase per P V product: O may be rescaled
-    uint64_t* o_done = bars + 14;     // one phase: the last P V product is complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t* pv_done = bars + 13;    // [2], by tile parity; a phase per P V product: O may be rescaled
+    uint64_t* o_done = bars + 15;     // one phase: the last P V product is complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,7 +158,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 128);
         }
-        mbar_init(pv_done, 1);
+        mbar_init(&pv_done[0], 1);
+        mbar_init(&pv_done[1], 1);
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -245,7 +246,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                      (jj > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&v_empty[s]);
-                    umma_commit(pv_done);
+                    umma_commit(&pv_done[jj & 1]);
                     if (jj == n - 1) umma_commit(o_done);
                 }
             }
@@ -307,7 +308,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             m_run = m_new;
             // O holds the sum up to tile j-1 relative to the old maximum: rescale this row when it moved
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-                ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (j - 1) & 1, abortp));
+                // the product of tile j-1; its barrier's phase before (tile j-3) is long complete, the
+                // one after (tile j+1) cannot begin before this warp has delivered P of tile j
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abortp));
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
@@ -340,10 +343,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(&p_full[s]);
         }
         pdl_trigger_gemm();
-        // Not pv_done: its phases are told apart by one parity bit, and here the product before the last
-        // may still be running (it was issued after the S that this warp just finished with), so a wait
-        // for the last phase's parity could pass two phases early.  Inside the loop a waiter is never more
-        // than one phase behind: the product two tiles back was issued before the S it has just read.
+        // A barrier of its own, with a single phase.  (A barrier shared with the loop's waits would be
+        // asked for a phase by its parity bit alone; the product before the last may still be running here -
+        // it was issued after the S that this warp just finished with - and such a wait once passed two
+        // phases early, about one step in ten under load.)
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0, abortp));
         if (ok) {
             tc_fence_after();
