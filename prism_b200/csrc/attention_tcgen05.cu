@@ -112,7 +112,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ cached_len, int nh, int nkv, int page_size, int num_pages, int window,
                        float scale_log2, int* err) {
     using C = ACfg<HD>;
-    pdl_trigger();
     pdl_wait();
     // Heads vary fastest, and later query tiles (which see more keys) come first: the longest CTAs of
     // all heads start together and the short ones fill the gaps; the heads of one kv group walk the
@@ -172,6 +171,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     volatile int* abortp = &abort_flag;
+    // Dependents may start from here on, not earlier: this CTA holds its tensor memory now, so a
+    // dependent CTA that allocates tensor memory and then waits for this grid cannot starve it.
+    pdl_trigger();
 
     if (warp == 0) {
         // ---- TMA producer ---------------------------------------------------------
