@@ -126,8 +126,7 @@ def bench_attn_decode(args):
 
 def bench_attn_prefill(args):
     Tn = args.tokens
-    kc, vc, bt, q, pos, seg, seg_start, cached, n_pages = paged_case(1, 0, Tn)
-    cached.zero_()
+    kc, vc, bt, q, pos, seg, seg_start, cached, n_pages = paged_case(1, args.cached, Tn)
     out = torch.empty(Tn, NH * HD, device=DEV, dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
     kern = ops.attention_prefill_bf16 if args.mma_sync else ops.attention_prefill_tc
@@ -138,8 +137,8 @@ def bench_attn_prefill(args):
         torch.cuda.synchronize()
         return
     t = timeit(fn)
-    fl = 4 * NH * HD * (Tn * (Tn + 1) / 2)
-    print(f"attn_prefill ({'mma.sync' if args.mma_sync else 'tcgen05'}) T={Tn}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s (causal flops)")
+    fl = 4 * NH * HD * (Tn * (Tn + 1) / 2 + Tn * args.cached)
+    print(f"attn_prefill ({'mma.sync' if args.mma_sync else 'tcgen05'}) T={Tn} cached={args.cached}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s (causal flops)")
 
 
 def bench_small(args):
@@ -176,6 +175,7 @@ if __name__ == "__main__":
     ap.add_argument("--bound", type=int, default=0, help="context bound used to choose the splits")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: CTAs per (token, kv head); 0 = the engine's choice")
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--cached", type=int, default=0, help="attn_prefill: tokens already in the cache before the portion")
     ap.add_argument("--mma-sync", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--once", action="store_true")
     a = ap.parse_args()
