@@ -270,6 +270,7 @@ TC_GEMM_MAX_M = int(os.environ.get("PRISM_TC_GEMM_MAX_M", "16"))
 
 
 # products with a long K (the down projection) stay on the tcgen05 kernel up to more tokens
+TC_KSPLIT_FORCED = int(os.environ.get("PRISM_TC_KSPLIT", "0"))       # experiments: a fixed K-split
 TC_GEMM_LONG_K = int(os.environ.get("PRISM_TC_GEMM_LONG_K", "8192"))
 TC_GEMM_MAX_M_LONG_K = int(os.environ.get("PRISM_TC_GEMM_MAX_M_LONG_K", "64"))    # batch 64 decode step: 4.79 -> 4.66 ms
 
@@ -290,9 +291,8 @@ def tc_ksplit(N: int, K: int) -> int:
     """CTAs that share one 128-row tile's K range: about one CTA per SM in all,
     at least 8 blocks of 64 k each."""
     tiles = (N + 127) // 128
-    forced = int(os.environ.get("PRISM_TC_KSPLIT", "0"))
-    if forced:
-        return forced
+    if TC_KSPLIT_FORCED:
+        return TC_KSPLIT_FORCED
     return max(1, min(NUM_SMS // tiles, ((K + 63) // 64) // 8))
 
 
