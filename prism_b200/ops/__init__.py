@@ -2,8 +2,10 @@
 
 Every function takes CUDA tensors, checks what the kernel assumes (dtype,
 contiguity, sizes), and launches on torch's current stream.  There is no CPU
-path and no library fallback: if the shared library cannot be built or
-loaded, or a tensor is not on a CUDA device, the call raises.
+path, and nothing steps in for a missing kernel: if the shared library cannot
+be built or loaded, or a tensor is not on a CUDA device, the call raises.
+(The one library call is by design, not a fallback: the bf16 matrix product
+of more than a few tokens, see ``linear``.)
 
 Which of andre-fu/prism's call sites each op replaces:
 
