@@ -163,10 +163,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     // Q rows of this kv head's group (rows >= g are zero), with plain loads: visible after the
     // first barrier of the loop below
+    const __nv_bfloat16* q_now = pdl_fresh(q);       // q is the previous kernel's output
     for (int i = tid; i < 16 * (HD / 8); i += ATT_THREADS) {
         const int r = i / (HD / 8), c = i % (HD / 8);
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < g) v = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + ((size_t)kvh * g + r) * HD + c * 8);
+        if (r < g) v = *reinterpret_cast<const uint4*>(q_now + (size_t)t * q_stride + ((size_t)kvh * g + r) * HD + c * 8);
         *reinterpret_cast<uint4*>(Qs + r * STRIDE + c * 8) = v;
     }
     __syncthreads();
@@ -361,8 +362,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
-    const float* po = part_o + (size_t)blockIdx.x * nsplit * HD;
-    const float* pml = part_ml + (size_t)blockIdx.x * nsplit * 2;
+    const float* po = pdl_fresh(part_o) + (size_t)blockIdx.x * nsplit * HD;       // the attention kernel's output
+    const float* pml = pdl_fresh(part_ml) + (size_t)blockIdx.x * nsplit * 2;
     float M = -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
     const float Mu = M == -INFINITY ? 0.f : M;

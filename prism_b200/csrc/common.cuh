@@ -38,6 +38,15 @@ namespace prism {
 // may be launched as soon as every CTA of this one has started.  Both are
 // no-ops for a kernel launched without the attribute.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// What the kernel before this one wrote must be read through pdl_fresh(pointer), taken after pdl_wait(),
+// never straight through a `const T* __restrict__` parameter: the compiler treats loads through such a
+// parameter as invariant for the whole kernel and may hoist them above the wait (the "memory" clobber
+// does not hold them back).  That happened: decode attention read the previous step's q from a CUDA
+// graph's static buffer.  The empty volatile asm makes the pointer a value produced after the wait.
+template <typename T> __device__ __forceinline__ T* pdl_fresh(T* p) {
+    asm volatile("" : "+l"(p)::"memory");
+    return p;
+}
 #ifndef PRISM_PDL_TRIGGER_SMALL
 #define PRISM_PDL_TRIGGER_SMALL 1
 #endif

@@ -12,7 +12,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ 
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    const int id = ids[t];
+    const int id = pdl_fresh(ids)[t];            // in pipelined decoding the ids are the sampler's output
     float* o = out + (size_t)t * H;
     if (id < 0 || id >= V) {
         if (threadIdx.x == 0) report_error(err, PRISM_ERR_TOKEN_RANGE);

@@ -16,12 +16,13 @@
 namespace prism {
 
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in,
                                    int nsplit, size_t split_stride,
                                    const void* __restrict__ weight, int weight_bf16, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int H) {
     pdl_trigger();
     pdl_wait();
+    const TD* delta = pdl_fresh(delta_in);          // the previous kernel's output
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -47,12 +48,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
 // 8 * ITERS values in registers between the sum of squares and the store, so
 // the row is read once.  One block per row, as above.
 template <typename TD, typename TO, int ITERS>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in,
                                        int nsplit, size_t split_stride,
                                        const void* __restrict__ weight, int weight_bf16, float eps,
                                        TO* __restrict__ out, const int* __restrict__ rows, int H) {
     pdl_trigger();
     pdl_wait();
+    const TD* delta = pdl_fresh(delta_in);          // the previous kernel's output
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;

@@ -99,14 +99,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 // the table.  A thread rotates 8 neighbouring pairs (two 16-byte accesses for
 // bf16), or copies 8 unrotated dims.
 template <typename T>
-__global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T* __restrict__ v,
+__global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T* __restrict__ v_in,
                                    int row_stride, const int* __restrict__ positions,
-                                   const int* __restrict__ tok_seg, const float2* __restrict__ table,
+                                   const int* __restrict__ tok_seg, const float2* __restrict__ table_in,
                                    int rd, T* __restrict__ kc, T* __restrict__ vc,
                                    const int* __restrict__ block_table, int bt_width, int page_size,
                                    int num_pages, int nh, int nkv, int hd, int max_pos, int* err) {
     pdl_trigger();
     pdl_wait();
+    const T* v = pdl_fresh(v_in);                      // outputs of the kernels before this one
+    const float2* table = pdl_fresh(table_in);
     const int t = blockIdx.x;
     const int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
@@ -174,15 +176,17 @@ __global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T
 // them so) plus an optional bias, and writing the rotated q to its own buffer.
 // Sum, bias and rotation in float32, one rounding at each store.
 template <typename T>
-__global__ void rope_kv_partial_kernel(const float* __restrict__ parts, int ks, size_t part_stride, int D,
+__global__ void rope_kv_partial_kernel(const float* __restrict__ parts_in, int ks, size_t part_stride, int D,
                                        const void* __restrict__ bias, int bias_bf16, T* __restrict__ q_out,
                                        int q_out_stride, const int* __restrict__ positions,
-                                       const int* __restrict__ tok_seg, const float2* __restrict__ table, int rd,
+                                       const int* __restrict__ tok_seg, const float2* __restrict__ table_in, int rd,
                                        T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ block_table,
                                        int bt_width, int page_size, int num_pages, int nh, int nkv, int hd,
                                        int max_pos, int* err) {
     pdl_trigger();
     pdl_wait();
+    const float* parts = pdl_fresh(parts_in);          // outputs of the kernels before this one
+    const float2* table = pdl_fresh(table_in);
     const int t = blockIdx.x;
     const int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {

@@ -21,7 +21,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     __shared__ float s_val[SAMPLE_THREADS];
     __shared__ int s_idx[SAMPLE_THREADS];
     const int row = blockIdx.x, tid = threadIdx.x;
-    const float* x = logits + (size_t)row * ld;
+    const float* x = pdl_fresh(logits) + (size_t)row * ld;       // the previous kernel's output
     const float temp = temperature ? temperature[row] : 0.f;
 
     // argmax (needed by both branches: it is also the softmax's max)
@@ -96,7 +96,7 @@ argmax_split_kernel(const float* __restrict__ logits, int ld, int V, float* __re
     const int nb = gridDim.x, b = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
     const int per = ((V + nb - 1) / nb + 3) & ~3;
     const int c0 = min(b * per, V), c1 = min(c0 + per, V);
-    const float* x = logits + (size_t)row * ld;
+    const float* x = pdl_fresh(logits) + (size_t)row * ld;       // the previous kernel's output
     float best = -INFINITY;
     int besti = V;
     for (int i = c0 + tid; i < c1; i += ARGMAX_THREADS) {

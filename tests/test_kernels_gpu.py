@@ -477,6 +477,9 @@ DECODE_CASES = [
     (16, 1, 64, 32, 100, [99, 100, 101, 700, 3], 7),
     (14, 2, 128, 8, 64, [1500, 64, 63], 64),
     (40, 8, 128, 256, None, [3000], 33),
+    (14, 2, 64, 256, None, [300, 17, 700, 64, 1] + [0] * 11, 9),        # a graph bucket of 16 with padded rows
+    (14, 2, 64, 256, None, [300, 17, 700, 64, 1], 11),
+    (12, 2, 128, 64, None, [129, 64, 1000, 0, 0, 0, 0, 0], 5),
 ]
 
 
