@@ -1,5 +1,6 @@
 """Layers of Qwen2.5-7B size (hidden 3584, 28/4 heads of 128, intermediate
-18944), two of them, with a reduced vocabulary so that the plain model can run
+18944) and of Qwen2.5-0.5B size (hidden 896, 14/2 heads of 64, intermediate 4864,
+tied head), two of each, with a reduced vocabulary so that the plain model can run
 on the CPU: the production kernels (tensor-core attention, the tcgen05 GEMM
 with its fused epilogues, the library GEMM for long portions) at the sizes
 they were written for, in float32 and bfloat16, whole and cut (GPU)."""
@@ -19,11 +20,15 @@ SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidd
                 max_position_embeddings=32768, use_sliding_window=False)
 
 
-@pytest.fixture(scope="module")
-def folder_and_plain():
+SHAPE_05B = dict(SHAPE_7B, hidden_size=896, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
+                 intermediate_size=4864, tie_word_embeddings=True)
+
+
+@pytest.fixture(scope="module", params=["7B", "0.5B"])
+def folder_and_plain(request):
     from prism_b200.weights.random_init import write_model_folder
     with tempfile.TemporaryDirectory(prefix="prism_7b_shape_") as d:
-        write_model_folder(SHAPE_7B, 3, d)
+        write_model_folder(SHAPE_7B if request.param == "7B" else SHAPE_05B, 3, d)
         cfg, t = P.load_folder(d)
         seqs = {"a": random_tokens(8192, 150, 1), "b": random_tokens(8192, 41, 2), "c": random_tokens(8192, 77, 3)}
         ref = {k: P.forward(cfg, t, v) for k, v in seqs.items()}
