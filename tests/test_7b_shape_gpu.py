@@ -35,22 +35,26 @@ def folder_and_plain(request):
         yield d, seqs, ref
 
 
-def runner_for(folder, dtype, num_pages, page_size=64):
+def runner_for(folder, dtype, num_pages, page_size=64, graphs=False):
     from prism_b200.engine.runner import ModelRunner
     from prism_b200.weights.loader import load_model_folder
     tdt = getattr(torch, dtype)
     _, model, pool = load_model_folder(folder, "cuda:0", tdt)
-    r = ModelRunner(model, "cuda:0", tdt, page_size, num_pages, 8)
+    r = ModelRunner(model, "cuda:0", tdt, page_size, num_pages, 8, max_seq_len=512, use_cuda_graph=graphs,
+                    graph_batch_sizes=(1, 4))
     r._pool = pool
     return r
 
 
 @pytest.mark.parametrize("dtype,atol,rtol", [("float32", 1e-3, 1e-4), ("bfloat16", 5e-3, 4e-2)])
-@pytest.mark.parametrize("mode", ["whole", "tail", "mixed"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "tail_graphs", "mixed", "mixed_graphs"])
 def test_7b_sized_layers(folder_and_plain, dtype, atol, rtol, mode):
+    """``*_graphs``: pure-decode steps are replayed from captured CUDA graphs, where the kernels
+    really overlap (programmatic dependent launch); the other modes launch kernel by kernel."""
     folder, seqs, ref = folder_and_plain
-    steps = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 12), "mixed": lambda s: trace_mixed(s, seed=5)}[mode](seqs)
-    runner = runner_for(folder, dtype, trace_budget(steps, 64) // 64)
+    kind = mode.split("_")[0]
+    steps = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 12), "mixed": lambda s: trace_mixed(s, seed=5)}[kind](seqs)
+    runner = runner_for(folder, dtype, trace_budget(steps, 64) // 64, graphs=mode.endswith("_graphs"))
     got = run_trace(runner, steps)
     worst = 0.0
     for rid, seq in seqs.items():
