@@ -16,13 +16,13 @@ TOL = {"float32": dict(atol=2e-5, rtol=1e-5), "bfloat16": dict(atol=2e-3, rtol=3
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71, 130], "C": [3, 30, 64, 97, 150], "D": [2, 65, 128, 200, 333]}
 
 
-def make_runner(name, dtype, num_pages, page_size=None, max_seqs=8):
+def make_runner(name, dtype, num_pages, page_size=None, max_seqs=8, graphs=False):
     from prism_b200.weights.loader import load_model_folder
     from prism_b200.engine.runner import ModelRunner
     tdt = getattr(torch, dtype)
     cfg, model, pool = load_model_folder(model_folder(name), "cuda:0", tdt)
     ps = page_size or TINY[name][2]
-    runner = ModelRunner(model, "cuda:0", tdt, ps, num_pages, max_seqs, use_cuda_graph=False)
+    runner = ModelRunner(model, "cuda:0", tdt, ps, num_pages, max_seqs, use_cuda_graph=graphs, graph_batch_sizes=(1, 2, 4))
     runner._pool = pool
     return runner
 
@@ -77,3 +77,18 @@ def test_replay_is_reproducible(name, dtype, ps):
     for _ in range(3):
         got = run_trace(runner, steps)
         assert all(torch.equal(got[k], ref[k]) for k in ref)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("mode", ["tail", "mixed"])
+def test_cutting_with_decode_graphs(name, dtype, mode):
+    """The same with pure-decode steps replayed from captured CUDA graphs (buckets 1, 2, 4 with
+    padded rows): inside a graph the kernels overlap, which launches from Python never do."""
+    seqs = sequences(name)
+    steps = {"tail": trace_tail, "mixed": lambda s: trace_mixed(s, seed=7)}[mode](seqs)
+    ps = TINY[name][2]
+    runner = make_runner(name, dtype, num_pages=trace_budget(steps, ps) // ps, graphs=True)
+    got = run_trace(runner, steps)
+    compare_with_plain(name, seqs, got, **TOL[dtype])
+    assert runner.cache.pages_in_use() == 0 and runner.graph_kernel_launches > 0
