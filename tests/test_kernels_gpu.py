@@ -535,6 +535,8 @@ PREFILL_TC_CASES = [
     (4, 2, 128, 64, None, [(0, 700)]),
     (6, 2, 128, 192, None, [(130, 300), (0, 127), (0, 128), (63, 129)]),
     (3, 1, 64, 64, 200, [(0, 517)]),
+    (4, 2, 128, 256, None, [(0, 3000)]),                 # 47 key tiles: the lazy rescale and both S buffers many times over
+    (2, 1, 64, 64, None, [(1000, 2100), (3000, 90)]),
 ]
 
 
