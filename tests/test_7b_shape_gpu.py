@@ -24,11 +24,15 @@ SHAPE_05B = dict(SHAPE_7B, hidden_size=896, num_attention_heads=14, num_key_valu
                  intermediate_size=4864, tie_word_embeddings=True)
 
 
-@pytest.fixture(scope="module", params=["7B", "0.5B"])
+# the upper layer sees a window of 100 positions (and lands in a cache group of its own)
+SHAPE_7B_WINDOW = dict(SHAPE_7B, use_sliding_window=True, sliding_window=100, max_window_layers=1)
+
+
+@pytest.fixture(scope="module", params=["7B", "0.5B", "7B-window"])
 def folder_and_plain(request):
     from prism_b200.weights.random_init import write_model_folder
     with tempfile.TemporaryDirectory(prefix="prism_7b_shape_") as d:
-        write_model_folder(SHAPE_7B if request.param == "7B" else SHAPE_05B, 3, d)
+        write_model_folder({"7B": SHAPE_7B, "0.5B": SHAPE_05B, "7B-window": SHAPE_7B_WINDOW}[request.param], 3, d)
         cfg, t = P.load_folder(d)
         seqs = {"a": random_tokens(8192, 150, 1), "b": random_tokens(8192, 41, 2), "c": random_tokens(8192, 77, 3)}
         ref = {k: P.forward(cfg, t, v) for k, v in seqs.items()}
@@ -63,6 +67,21 @@ def test_7b_sized_layers(folder_and_plain, dtype, atol, rtol, mode):
             err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
             worst = max(worst, err)
             assert err <= atol + rtol * scale, (rid, pos, err, scale)
+    assert runner.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_7b_sized_layers_with_pages_of_256(folder_and_plain, graphs):
+    """The benchmark's page size: a whole sequence, then its last tokens one by one."""
+    folder, seqs, ref = folder_and_plain
+    steps = trace_tail(seqs, 10)
+    runner = runner_for(folder, "bfloat16", trace_budget(steps, 256) // 256, page_size=256, graphs=graphs)
+    got = run_trace(runner, steps)
+    for rid, seq in seqs.items():
+        scale = float(ref[rid].abs().max())
+        for pos in range(len(seq)):
+            err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
+            assert err <= 5e-3 + 4e-2 * scale, (rid, pos, err, scale)
     assert runner.cache.pages_in_use() == 0
 
 
