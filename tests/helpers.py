@@ -157,9 +157,10 @@ def trace_budget(steps, unit: int) -> int:
     return best
 
 
-def run_trace(runner, steps):
+def run_trace(runner, steps, before_step=None):
     """Drive a ModelRunner through a trace in-process.  Returns
-    ``{(request id, position): logits row (float32 CPU tensor)}``."""
+    ``{(request id, position): logits row (float32 CPU tensor)}``.
+    ``before_step()`` is called before every step (e.g. to keep the GPU busy)."""
     from prism_b200.engine.batch import Segment
     out, live, fed = {}, set(), {}
     for st in steps:
@@ -170,6 +171,8 @@ def run_trace(runner, steps):
                 live.add(e["id"])
                 fed[e["id"]] = 0
             segs.append(Segment(e["id"], e["tokens"], e["want"]))
+        if before_step is not None:
+            before_step()
         logits = runner.step(segs)
         if logits is not None:
             logits = logits.float().cpu()

@@ -51,15 +51,24 @@ def runner_for(folder, dtype, num_pages, page_size=64, graphs=False):
 
 
 @pytest.mark.parametrize("dtype,atol,rtol", [("float32", 1e-3, 1e-4), ("bfloat16", 5e-3, 4e-2)])
-@pytest.mark.parametrize("mode", ["whole", "tail", "tail_graphs", "mixed", "mixed_graphs"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "tail_graphs", "mixed", "mixed_graphs", "whole_backlog", "mixed_backlog"])
 def test_7b_sized_layers(folder_and_plain, dtype, atol, rtol, mode):
     """``*_graphs``: pure-decode steps are replayed from captured CUDA graphs, where the kernels
-    really overlap (programmatic dependent launch); the other modes launch kernel by kernel."""
+    really overlap (programmatic dependent launch); ``*_backlog``: a few milliseconds of other work are
+    queued before every step, so that the step's kernels wait in the queue and then run back to back,
+    overlapping as well; the other modes launch kernel by kernel into an idle GPU."""
     folder, seqs, ref = folder_and_plain
     kind = mode.split("_")[0]
     steps = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 12), "mixed": lambda s: trace_mixed(s, seed=5)}[kind](seqs)
     runner = runner_for(folder, dtype, trace_budget(steps, 64) // 64, graphs=mode.endswith("_graphs"))
-    got = run_trace(runner, steps)
+    busy = None
+    if mode.endswith("_backlog"):
+        big = torch.randn(8192, 8192, device="cuda:0", dtype=torch.bfloat16)
+
+        def busy():
+            for _ in range(4):
+                torch.mm(big, big)
+    got = run_trace(runner, steps, before_step=busy)
     worst = 0.0
     for rid, seq in seqs.items():
         scale = float(ref[rid].abs().max())

@@ -92,3 +92,21 @@ def test_cutting_with_decode_graphs(name, dtype, mode):
     got = run_trace(runner, steps)
     compare_with_plain(name, seqs, got, **TOL[dtype])
     assert runner.cache.pages_in_use() == 0 and runner.graph_kernel_launches > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_cutting_behind_a_backlog(name, dtype):
+    """Mixed steps launched into a busy GPU: the step's kernels wait in the queue and then run
+    back to back, so that programmatic dependent launch really overlaps them."""
+    seqs = sequences(name)
+    steps = trace_mixed(seqs, seed=7)
+    ps = TINY[name][2]
+    runner = make_runner(name, dtype, num_pages=trace_budget(steps, ps) // ps)
+    big = torch.randn(4096, 4096, device="cuda:0")
+
+    def busy():
+        for _ in range(3):
+            torch.mm(big, big)
+    got = run_trace(runner, steps, before_step=busy)
+    compare_with_plain(name, seqs, got, **TOL[dtype])
