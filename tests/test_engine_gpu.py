@@ -146,6 +146,31 @@ def test_decoding_requests_beside_a_prompt_portion(name, monkeypatch):
         near_greedy(name, p, r.generated_tokens, 0.03)
 
 
+@pytest.mark.parametrize("graph,pipelined", [(False, False), (True, False), (False, True), (True, True)])
+def test_eos_ends_requests_at_different_times(graph, pipelined):
+    """An end-of-sequence token that some requests produce early, some late and some never:
+    every request ends where the plain model's does (the token itself is kept), with and without
+    decode graphs and pipelined decoding (where a request's next token is already in flight when
+    its end is seen, and is dropped)."""
+    from prism_b200 import Engine, EngineConfig, SamplingParams, SchedulerConfig
+    cfg, t = plain_model("A")
+    prompts = [random_tokens(256, n, 500 + n) for n in (5, 9, 14, 6, 11, 20, 3)]
+    full = [P.generate(cfg, t, p, 24) for p in prompts]
+    counts = {}
+    for g in full:
+        for tok in set(g[2:]):
+            counts[tok] = counts.get(tok, 0) + 1
+    eos = max(counts, key=lambda k: (counts[k], -k))          # the token most requests meet somewhere
+    want = [g[:g.index(eos) + 1] if eos in g else g for g in full]
+    ec = EngineConfig(kv_page_size=16, num_pages=64, use_cuda_graph=graph, graph_batch_sizes=(1, 2, 4, 8),
+                      scheduler=SchedulerConfig(async_decode=pipelined))
+    eng = Engine(model_folder("A"), ec, dtype="float32")
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=24, eos_token_id=eos))
+    assert [r.token_ids for r in res] == want
+    assert [r.finish_reason for r in res] == ["stop" if eos in g else "length" for g in full]
+    assert eng.runner.cache.pages_in_use() == 0
+
+
 def test_bad_token_id_is_reported_not_faulted():
     from prism_b200 import SamplingParams
     from prism_b200.engine.runner import DeviceError
