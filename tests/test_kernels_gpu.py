@@ -265,6 +265,20 @@ def test_swiglu(T, I, dtype):
     assert torch.allclose(out.float(), ref, atol=tol, rtol=tol)
 
 
+def test_rope_table_at_far_positions():
+    """cos/sin of position x inverse frequency in float32 with full range reduction: angles of
+    tens of thousands of radians (position 131,071, theta 1e6) still match the CPU's."""
+    ops = _ops()
+    hd, theta = 128, 1e6
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    pos = torch.tensor([0, 1, 77, 4095, 32767, 131071], dtype=torch.int32)
+    table = torch.empty(pos.shape[0], hd // 2, 2, device=DEV)
+    ops.rope_table(pos.to(DEV), inv.to(DEV), table)
+    ang = torch.outer(pos.float(), inv)                       # float32 product, as andre-fu/prism forms it
+    assert torch.allclose(table[..., 0].cpu(), torch.cos(ang), atol=2e-6, rtol=0)
+    assert torch.allclose(table[..., 1].cpu(), torch.sin(ang), atol=2e-6, rtol=0)
+
+
 @pytest.mark.parametrize("nh,nkv,hd,rd,P", [(5, 1, 48, 48, 8), (28, 4, 128, 128, 256), (6, 3, 80, 32, 16), (2, 2, 16, 0, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("use_table", [False, True])
