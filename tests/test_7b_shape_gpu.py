@@ -155,3 +155,34 @@ def test_decode_graph_replay_gives_the_eager_logits(size):
     for a, b in zip(logits[False], logits[True]):
         # the two differ by rounding only (the graph splits the keys over a different number of CTAs)
         assert float((a - b).abs().max()) <= 0.03 * float(a.abs().max()), float((a - b).abs().max())
+
+
+def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypatch):
+    """6,000 tokens (too long for the plain model on the CPU): the tcgen05 prefill attention and the
+    split-KV decode attention against the shape-generic kernel, which shares no code with them, whole
+    and in portions of 1,024, followed by a few decode steps through graphs."""
+    from prism_b200 import Engine, EngineConfig, ops
+    from prism_b200.engine.batch import Segment
+    cfg = dict(SHAPE_7B, vocab_size=152064)
+    prompt = random_tokens(150000, 6000, 4)
+    logits = {}
+    for mode in ("fast", "generic", "portions"):
+        monkeypatch.setattr(ops, "FORCE_GENERIC_ATTENTION", mode == "generic")
+        eng = Engine(None, EngineConfig(kv_page_size=256, num_pages=32, max_seq_len=8192, use_cuda_graph=mode != "generic"),
+                     dtype="bfloat16", config=cfg, random_seed=0)
+        r = eng.runner
+        r.begin_request(0)
+        if mode == "portions":
+            for c in range(0, 6000, 1024):
+                part = prompt[c:c + 1024]
+                lg = r.step([Segment(0, part, [len(part) - 1])])
+        else:
+            lg = r.step([Segment(0, prompt, [5999])])
+        outs = [lg.float().cpu()] + [r.step([Segment(0, [100 + s], [0])]).float().cpu() for s in range(4)]
+        r.check_errors()
+        logits[mode] = outs
+        del eng, r
+    scale = float(logits["fast"][0].abs().max())
+    for mode in ("generic", "portions"):
+        for a, b in zip(logits["fast"], logits[mode]):
+            assert float((a - b).abs().max()) <= 0.03 * scale, (mode, float((a - b).abs().max()), scale)
