@@ -224,10 +224,12 @@ class Scheduler:
 
     # ---- pipelined decoding ---------------------------------------------------------
     def _steady(self) -> bool:
-        """Only decoding requests, nobody waiting: the next steps have the same
-        rows in the same order, so a step can be launched before the previous
-        step's tokens have been read."""
-        return (self.config.async_decode and hasattr(self.sampler, "sample_async") and not self.waiting
+        """Only decoding requests, and nobody who could be admitted (nobody waiting, or no
+        place for another request until one finishes): the next steps have the same rows in the
+        same order, so a step can be launched before the previous step's tokens have been read."""
+        nobody_to_admit = (not self.waiting or len(self.running) >= self.config.max_num_seqs
+                           or not self.cache.has_free_slot())
+        return (self.config.async_decode and hasattr(self.sampler, "sample_async") and nobody_to_admit
                 and bool(self.running) and len(self.running) <= self.config.max_batch_tokens
                 and all(r.remaining == 1 and r.generated_tokens for r in self.running))
 

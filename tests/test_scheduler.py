@@ -167,3 +167,79 @@ def test_sampling_counter_is_the_number_of_generated_tokens():
     assert all(0.0 <= uniform(s, r, i) < 1.0 for s in range(3) for r in range(3) for i in range(50))
     mean = sum(uniform(1, 0, i) for i in range(4000)) / 4000
     assert abs(mean - 0.5) < 0.03
+
+
+# --------------------------------------------------------------------------
+# pipelined decoding with stand-ins: the next step takes its tokens from the
+# sampler's output of the step before, which the host has not read yet
+# --------------------------------------------------------------------------
+
+class PipelinedRunner(FakeRunner):
+    def can_run(self, segments):
+        return all(self.cache.can_append(s.req_id, len(s.tokens)) for s in segments)
+
+    def step(self, segments, token_source=None):
+        if token_source is not None:                       # "device" tokens of the step in flight
+            for s, tok in zip(segments, token_source):
+                s.tokens = [int(tok)]
+        return super().step(segments)
+
+
+class PipelinedSampler(FakeSampler):
+    class Handle:
+        def __init__(self, tokens):
+            self.device_tokens = tokens
+
+    def __init__(self):
+        self.async_steps = 0
+
+    def sample_async(self, logits, temps, us):
+        self.async_steps += 1
+        return self.Handle([int(r.argmax()) for r in logits])
+
+    def read(self, handle):
+        return list(handle.device_tokens)
+
+
+def make_pipelined(num_pages=64, **kw):
+    runner = PipelinedRunner(num_pages, **{k: v for k, v in kw.items() if k in ("page_size", "max_seqs", "max_seq_len")})
+    cfg = SchedulerConfig(**{k: v for k, v in kw.items() if k in ("max_batch_tokens", "max_num_seqs", "prefill_chunk")})
+    sampler = PipelinedSampler()
+    return Scheduler(runner, sampler, cfg, eos_token_id=kw.get("eos")), runner, sampler
+
+
+def test_pipelined_decoding_gives_the_same_tokens():
+    s, runner, sampler = make_pipelined(max_num_seqs=4)
+    prompts = [[3, 1, 4], [1, 5, 9, 2, 6], [5, 3], [5, 8, 9, 7]]
+    lens = [9, 4, 12, 7]
+    reqs = [s.add_request(p, SamplingParams(max_new_tokens=n)) for p, n in zip(prompts, lens)]
+    s.run_to_completion()
+    assert [r.generated_tokens for r in reqs] == [expected(p, n) for p, n in zip(prompts, lens)]
+    assert sampler.async_steps > 0 and runner.cache.pages_in_use() == 0
+    runner.cache.check_invariants()
+
+
+def test_pipelined_decoding_goes_on_while_waiting_requests_have_no_place():
+    """Two places, five requests: while both places are taken nobody can be admitted, so decoding is
+    pipelined although requests wait; every time a request ends the pipeline drains and the next is admitted."""
+    s, runner, sampler = make_pipelined(max_num_seqs=2)
+    prompts = [[i + 1, i + 2, i + 3] for i in range(5)]
+    reqs = [s.add_request(p, SamplingParams(max_new_tokens=6 + i)) for i, p in enumerate(prompts)]
+    s.run_to_completion()
+    assert [r.generated_tokens for r in reqs] == [expected(p, 6 + i) for i, p in enumerate(prompts)]
+    total = sum(6 + i for i in range(5))
+    assert sampler.async_steps >= total // 2 // 2            # most decode steps went through the pipeline
+    assert max(len(step) for step in runner.steps) <= 2 and runner.cache.pages_in_use() == 0
+
+
+def test_pipelined_decoding_stops_at_eos_and_drops_the_token_in_flight():
+    prompt = [2, 7, 1]
+    eos = expected(prompt, 5)[4]
+    s, runner, sampler = make_pipelined(eos=eos)
+    a = s.add_request(prompt, SamplingParams(max_new_tokens=20))
+    b = s.add_request([9, 9], SamplingParams(max_new_tokens=8, ignore_eos=True))
+    s.run_to_completion()
+    want_a = expected(prompt, 20)
+    assert a.generated_tokens == want_a[:want_a.index(eos) + 1] and a.finish_reason == "stop"
+    assert b.generated_tokens == expected([9, 9], 8) and b.finish_reason == "length"
+    assert runner.cache.pages_in_use() == 0
