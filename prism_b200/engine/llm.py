@@ -12,13 +12,11 @@ temperature is given - for a list of prompts batched continuously.
 
 from __future__ import annotations
 
-import json
-import os
 from typing import List, Optional, Sequence, Union
 
 import torch
 
-from ..config.engine_config import EngineConfig, ModelConfig, SchedulerConfig
+from ..config.engine_config import EngineConfig, ModelConfig
 from ..config.model_config import read_config_json
 from ..model_registry import build_model
 from ..sampling.sampler import Sampler, SamplingParams

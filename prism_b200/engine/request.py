@@ -5,7 +5,6 @@ recomputed from its prompt plus what it has generated."""
 
 from __future__ import annotations
 
-import time
 from dataclasses import dataclass, field
 from enum import Enum
 from typing import List, Optional

@@ -16,7 +16,7 @@ position 0 and the scratch page and their logits are dropped.
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import torch
 

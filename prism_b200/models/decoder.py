@@ -7,8 +7,8 @@ the spec.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from dataclasses import dataclass
+from typing import List, Optional
 
 from ..parts.base import CacheNeed, Part, PartSpec, build_part
 

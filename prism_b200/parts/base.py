@@ -24,7 +24,7 @@ prefix for its tensors and nothing else.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 
 # --------------------------------------------------------------------------

@@ -16,7 +16,6 @@ from typing import List, Optional, Sequence
 
 import torch
 
-from .rng import uniform
 from .. import ops
 
 

@@ -16,7 +16,7 @@ import glob
 import json
 import os
 import struct
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

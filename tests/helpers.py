@@ -8,7 +8,6 @@ import random
 import sys
 import tempfile
 
-import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))

@@ -20,7 +20,6 @@ are implemented: ``head_dim`` as an explicit key and the sliding window
 from __future__ import annotations
 
 import json
-import math
 import os
 
 import torch

@@ -10,7 +10,7 @@ from safetensors.torch import load_file, save_file
 from helpers import TINY_A, TINY_B, TINY_C, model_folder
 
 from prism_b200.config.model_config import ConfigError, Qwen2Config
-from prism_b200.model_registry import build_model, register_architecture, registered_architectures, resolve
+from prism_b200.model_registry import build_model, registered_architectures, resolve
 from prism_b200.weights.loader import WeightError, load_model_folder
 from prism_b200.weights.random_init import file_tensors, write_model_folder
 

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 from helpers import (P, TINY, compare_with_plain, model_folder, plain_logits, plain_model, random_tokens,
-                     trace_budget, trace_mixed, trace_tail)
+                     trace_budget, trace_mixed)
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

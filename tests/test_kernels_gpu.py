@@ -1,7 +1,6 @@
 """Each CUDA kernel alone against a plain PyTorch float32 reference of the same
 op, at sizes other than the tiny engine configurations use (GPU)."""
 
-import math
 
 import pytest
 import torch
