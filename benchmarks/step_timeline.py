@@ -3,7 +3,7 @@ CUDA activity records that torch.profiler collects (no serialisation, no replays
 overlap as they do in production, so a kernel that was launched early and sat in its dependency
 wait shows a long duration and a negative gap).
 
-    python benchmarks/step_timeline.py [--batch 8] [--layers 28] [--context 2048]
+    python benchmarks/step_timeline.py [--batch 8] [--layers 28] [--context 2048] [--shape 7b|14b|32b]
 
 Prints the kernels of the first two layers and of the step's end, then one layer's critical path:
 for every kernel, how long after the end of the kernel before it its own end comes.
@@ -16,6 +16,7 @@ import sys
 import torch
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from bench import QWEN25_7B  # noqa: E402
 from prism_b200 import Engine, EngineConfig, SchedulerConfig, ops  # noqa: E402
 from prism_b200.engine.batch import Segment  # noqa: E402
@@ -26,9 +27,13 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--shape", default="7b", choices=["7b", "14b", "32b"], help="layer sizes (Qwen2.5-7B / 14B / 32B)")
     args = ap.parse_args()
     B = args.batch
     cfg = dict(QWEN25_7B, num_hidden_layers=args.layers)
+    if args.shape != "7b":
+        from workloads import SHAPES
+        cfg.update(SHAPES[args.shape], num_hidden_layers=args.layers)
     pages = (args.context + 256) // 256 + 1
     ec = EngineConfig(kv_page_size=256, num_pages=B * pages + 8, max_seq_len=4096, use_cuda_graph=True,
                       graph_batch_sizes=(B,), scheduler=SchedulerConfig(max_num_seqs=B))

@@ -56,8 +56,10 @@ def main():
     eng = Engine(None, ec, dtype="bfloat16", config=cfg, random_seed=0)
     prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
     sp = SamplingParams(max_new_tokens=new, ignore_eos=True)
-    # warm the decode graphs outside the timed run
-    eng.generate([p[:16] for p in prompts], SamplingParams(max_new_tokens=4, ignore_eos=True))
+    # capture the decode graphs of every bucket before the timed run, as a server does when it starts
+    for b in ec.graph_batch_sizes:
+        if b <= len(prompts):
+            eng.generate([p[:16] for p in prompts[:b]], SamplingParams(max_new_tokens=3, ignore_eos=True))
     steps0, pre0 = eng.stats.steps, eng.stats.preemptions
     torch.cuda.synchronize()
     t0 = time.perf_counter()

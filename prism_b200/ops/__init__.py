@@ -187,7 +187,7 @@ USE_GEMV = os.environ.get("PRISM_GEMV", "1") != "0"
 # the plain (bias) epilogue is slower than the library product at most decode shapes on B200 and is
 # opt-in; the paired-SwiGLU epilogue saves the [M, 2I] round trip and a launch and is the default
 USE_GEMV_PLAIN = os.environ.get("PRISM_GEMV_PLAIN", "0") == "1"
-GEMV_MAX_M = 32
+GEMV_MAX_M = int(os.environ.get("PRISM_GEMV_MAX_M", "16"))      # above 16 tokens it streams at half the bandwidth
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 
 
@@ -272,15 +272,19 @@ TC_GEMM_MAX_M = int(os.environ.get("PRISM_TC_GEMM_MAX_M", "16"))
 
 
 # products with a long K (the down projection) stay on the tcgen05 kernel up to more tokens
+# the fused gate/up + SwiGLU product stays on it up to 64 tokens: 14B layer sizes at batch 32, 8 layers + head:
+# 1.66 ms against 1.67 ms with the library product + SwiGLU kernel (and 2.00 ms with the mma.sync small-M GEMM)
+TC_GEMM_MAX_M_SWIGLU = int(os.environ.get("PRISM_TC_GEMM_MAX_M_SWIGLU", "64"))
 TC_KSPLIT_FORCED = int(os.environ.get("PRISM_TC_KSPLIT", "0"))       # experiments: a fixed K-split
 TC_GEMM_LONG_K = int(os.environ.get("PRISM_TC_GEMM_LONG_K", "8192"))
 TC_GEMM_MAX_M_LONG_K = int(os.environ.get("PRISM_TC_GEMM_MAX_M_LONG_K", "64"))    # batch 64 decode step: 4.79 -> 4.66 ms
 
 
-def tc_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 weight-streaming product takes this call."""
+def tc_gemm_ok(x: torch.Tensor, w: torch.Tensor, max_m: Optional[int] = None) -> bool:
+    """Whether the tcgen05 weight-streaming product takes this call (``max_m``: a caller's own
+    limit on the tokens, instead of the general one)."""
     M, K = x.shape
-    limit = TC_GEMM_MAX_M
+    limit = TC_GEMM_MAX_M if max_m is None else max_m
     if K >= TC_GEMM_LONG_K:
         limit = max(limit, TC_GEMM_MAX_M_LONG_K)
     return (USE_TC_GEMM and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= limit
@@ -753,7 +757,7 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
 def feed_forward_swiglu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor):
     """``down(silu(gate(x)) * up(x))`` with the fused gate/up weight."""
     M, I = x.shape[0], gate_up_w.shape[0] // 2
-    if tc_gemm_ok(x, gate_up_w):
+    if tc_gemm_ok(x, gate_up_w, TC_GEMM_MAX_M_SWIGLU):
         act = ctx.alloc((M, I), x.dtype)
         gemm_tc(x, gate_up_w, None, act, EPI_SWIGLU)       # gate/up product with the SwiGLU in its epilogue
         return linear_delta(act, down_w)
