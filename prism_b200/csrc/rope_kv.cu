@@ -132,7 +132,8 @@ __global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T
     const int per_k = rot_chunks + pass_chunks;
     const int n_q = nh * rot_chunks, n_k = nkv * per_k, n_v = nkv * (hd / 8);
     const float2* tab = table + (size_t)t * half;
-    for (int i = threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x) {
+    // gridDim.y CTAs share a token's items (few tokens: more CTAs, shorter latency chain)
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x * gridDim.y) {
         if (i < n_q + n_k) {
             const bool is_q = i < n_q;
             const int ii = is_q ? i : i - n_q;
@@ -307,13 +308,16 @@ PRISM_EXPORT int prism_rope_kv_write(void* q, void* k, const void* v, int dtype,
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
     if (table != nullptr && hd % 8 == 0 && rotary_dim % 16 == 0 && row_stride % 8 == 0) {
         const int items = (nh + nkv) * (hd / 2 / 8) + nkv * (hd / 8) + nkv * ((hd - rotary_dim) / 8);
-        const int vthreads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+        // up to 128 tokens: four CTAs of 64-128 threads per token instead of one of 256
+        const int parts = (T <= 128 && items >= 256) ? 4 : 1;
+        const int per_cta = (items + parts - 1) / parts;
+        const int vthreads = per_cta >= 256 ? 256 : (per_cta + 31) / 32 * 32;
         if (dtype == PRISM_DTYPE_BF16)
-            return (int)prism::launch_kernel(prism::rope_kv_vec_kernel<__nv_bfloat16>, dim3(T), dim3(vthreads), 0, stream,
+            return (int)prism::launch_kernel(prism::rope_kv_vec_kernel<__nv_bfloat16>, dim3(T, parts), dim3(vthreads), 0, stream,
                 (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride, positions,
                 tok_seg, (const float2*)table, rotary_dim, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc,
                 block_table, bt_width, page_size, num_pages, nh, nkv, hd, max_pos, err);
-        return (int)prism::launch_kernel(prism::rope_kv_vec_kernel<float>, dim3(T), dim3(vthreads), 0, stream,
+        return (int)prism::launch_kernel(prism::rope_kv_vec_kernel<float>, dim3(T, parts), dim3(vthreads), 0, stream,
                 (float*)q, (float*)k, (const float*)v, row_stride, positions, tok_seg,
                 (const float2*)table, rotary_dim, (float*)kc, (float*)vc, block_table, bt_width,
                 page_size, num_pages, nh, nkv, hd, max_pos, err);
