@@ -48,11 +48,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
 // 8 * ITERS values in registers between the sum of squares and the store, so
 // the row is read once.  One block per row, as above.
 template <typename TD, typename TO, int ITERS>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in,
+__global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta_in,
                                        int nsplit, size_t split_stride,
                                        const void* __restrict__ weight, int weight_bf16, float eps,
                                        TO* __restrict__ out, const int* __restrict__ rows, int H) {
     pdl_trigger();
+    // the norm's weight is a constant: it is in registers before the kernels before this one have ended
+    float w[ITERS][8];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (threadIdx.x + it * blockDim.x) * 8;
+        if (c < H) load_param8(weight, weight_bf16, c, w[it]);
+    }
     pdl_wait();
     const TD* delta = pdl_fresh(delta_in);          // the previous kernel's output
     __shared__ float scratch[33];
@@ -86,11 +93,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
     for (int it = 0; it < ITERS; ++it) {
         const int c = (threadIdx.x + it * blockDim.x) * 8;
         if (c < H) {
-            float w[8];
-            load_param8(weight, weight_bf16, c, w);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) w[k] *= v[it][k] * inv;
-            store8(o + c, w);
+            for (int k = 0; k < 8; ++k) w[it][k] *= v[it][k] * inv;
+            store8(o + c, w[it]);
         }
     }
 }

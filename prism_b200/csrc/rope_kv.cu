@@ -106,26 +106,26 @@ __global__ void rope_kv_vec_kernel(T* __restrict__ q, T* __restrict__ k, const T
                                    const int* __restrict__ block_table, int bt_width, int page_size,
                                    int num_pages, int nh, int nkv, int hd, int max_pos, int* err) {
     pdl_trigger();
-    pdl_wait();
-    const T* v = pdl_fresh(v_in);                      // outputs of the kernels before this one
-    const float2* table = pdl_fresh(table_in);
+    // The step's own inputs (positions, segments, block table) were complete before its first kernel
+    // started: the chain position -> page -> slot is followed while the kernels before this one still run.
     const int t = blockIdx.x;
     const int pos = positions[t];
-    if (pos < 0 || pos >= max_pos) {
-        if (threadIdx.x == 0) report_error(err, PRISM_ERR_POSITION_RANGE);
-        return;
-    }
+    const bool pos_ok = pos >= 0 && pos < max_pos;
     size_t slot = 0;
-    bool store = kc != nullptr;
-    if (store) {
+    bool store = kc != nullptr, page_ok = true;
+    if (store && pos_ok) {
         const int page = block_table[(size_t)tok_seg[t] * bt_width + pos / page_size];
-        if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
-            store = false;
-        } else {
-            slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
-        }
+        page_ok = page >= 0 && page < num_pages;
+        if (page_ok) slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
+        else store = false;
     }
+    pdl_wait();
+    if (!pos_ok || !page_ok) {
+        if (threadIdx.x == 0) report_error(err, pos_ok ? PRISM_ERR_PAGE_RANGE : PRISM_ERR_POSITION_RANGE);
+        if (!pos_ok) return;
+    }
+    const T* v = pdl_fresh(v_in);                      // outputs of the kernels before this one
+    const float2* table = pdl_fresh(table_in);
     const int half = rd / 2;
     const int rot_chunks = half / 8;                   // chunks of 8 rotated pairs per head
     const int pass_chunks = (hd - rd) / 8;             // chunks of 8 unrotated dims per head
@@ -185,43 +185,56 @@ __global__ void rope_kv_partial_kernel(const float* __restrict__ parts_in, int k
                                        int bt_width, int page_size, int num_pages, int nh, int nkv, int hd,
                                        int max_pos, int* err) {
     pdl_trigger();
-    pdl_wait();
-    const float* parts = pdl_fresh(parts_in);          // outputs of the kernels before this one
-    const float2* table = pdl_fresh(table_in);
+    // The step's own inputs (positions, segments, block table) were complete before its first kernel
+    // started: the chain position -> page -> slot is followed, and the bias brought into L2, while the
+    // kernels before this one still run.
     const int t = blockIdx.x;
     const int pos = positions[t];
-    if (pos < 0 || pos >= max_pos) {
-        if (threadIdx.x == 0) report_error(err, PRISM_ERR_POSITION_RANGE);
-        return;
-    }
+    const bool pos_ok = pos >= 0 && pos < max_pos;
     size_t slot = 0;
-    bool store = kc != nullptr;
-    if (store) {
+    bool store = kc != nullptr, page_ok = true;
+    if (store && pos_ok) {
         const int page = block_table[(size_t)tok_seg[t] * bt_width + pos / page_size];
-        if (page < 0 || page >= num_pages) {
-            if (threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
-            store = false;
-        } else {
-            slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
-        }
+        page_ok = page >= 0 && page < num_pages;
+        if (page_ok) slot = ((size_t)page * page_size + (pos % page_size)) * (size_t)nkv * hd;
+        else store = false;
     }
+    if (bias != nullptr && blockIdx.x == 0) {
+        const size_t bias_bytes = (size_t)D * (bias_bf16 ? 2 : 4);
+        for (size_t b = ((size_t)blockIdx.y * blockDim.x + threadIdx.x) * 128; b < bias_bytes;
+             b += (size_t)blockDim.x * gridDim.y * 128)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(bias) + b));
+    }
+    pdl_wait();
+    if (!pos_ok || !page_ok) {
+        if (threadIdx.x == 0) report_error(err, pos_ok ? PRISM_ERR_PAGE_RANGE : PRISM_ERR_POSITION_RANGE);
+        if (!pos_ok) return;
+    }
+    const float* parts = pdl_fresh(parts_in);          // outputs of the kernels before this one
+    const float2* table = pdl_fresh(table_in);
     auto load_sum8 = [&](int col, float (&v)[8]) {
         if (bias != nullptr) load_param8(bias, bias_bf16, col, v);
         else
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] = 0.f;
-        for (int s = 0; s < ks; ++s) {
-            float p[8];
-            load8(parts + (size_t)s * part_stride + (size_t)t * D + col, p);
+        // four splits' loads in flight together; the additions stay in the order s = 0, 1, ...
+        for (int s0 = 0; s0 < ks; s0 += 4) {
+            float p[4][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += p[e];
+            for (int u = 0; u < 4; ++u)
+                if (s0 + u < ks) load8(parts + (size_t)(s0 + u) * part_stride + (size_t)t * D + col, p[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (s0 + u < ks)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] += p[u][e];
         }
     };
     const int half = rd / 2;
     const int rot_chunks = half / 8, pass_chunks = (hd - rd) / 8, per = rot_chunks + pass_chunks;
     const int n_q = nh * per, n_k = nkv * per, n_v = nkv * (hd / 8);
     const float2* tab = table + (size_t)t * half;
-    for (int i = threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n_q + n_k + n_v; i += blockDim.x * gridDim.y) {
         if (i < n_q + n_k) {
             const bool is_q = i < n_q;
             if (!is_q && !store) continue;
@@ -282,15 +295,20 @@ PRISM_EXPORT int prism_rope_kv_write_partial(const float* parts, int ks, const v
         return (int)cudaErrorInvalidValue;
     const int D = (nh + 2 * nkv) * hd;
     const int items = (nh + nkv) * ((hd - rotary_dim / 2) / 8) + nkv * (hd / 8);
-    const int threads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+    // a few tokens: several CTAs of 32-64 threads per token, about 64 CTAs in all, instead of one of 256
+    int cta_per_tok = 1;
+    while (cta_per_tok < 8 && T * cta_per_tok < 64 && items / (cta_per_tok * 2) >= 32) cta_per_tok *= 2;
+    const int per_cta = (items + cta_per_tok - 1) / cta_per_tok;
+    const int threads = per_cta >= 256 ? 256 : (per_cta + 31) / 32 * 32;
+    const dim3 grid(T, cta_per_tok);
     const int bb = bias_dtype == PRISM_DTYPE_BF16;
     if (dtype == PRISM_DTYPE_BF16)
-        return (int)prism::launch_kernel(prism::rope_kv_partial_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+        return (int)prism::launch_kernel(prism::rope_kv_partial_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
                                          parts, ks, (size_t)T * D, D, bias, bb, (__nv_bfloat16*)q_out, q_out_stride,
                                          positions, tok_seg, (const float2*)table, rotary_dim, (__nv_bfloat16*)kc,
                                          (__nv_bfloat16*)vc, block_table, bt_width, page_size, num_pages, nh, nkv, hd,
                                          max_pos, err);
-    return (int)prism::launch_kernel(prism::rope_kv_partial_kernel<float>, dim3(T), dim3(threads), 0, stream, parts, ks,
+    return (int)prism::launch_kernel(prism::rope_kv_partial_kernel<float>, grid, dim3(threads), 0, stream, parts, ks,
                                      (size_t)T * D, D, bias, bb, (float*)q_out, q_out_stride, positions, tok_seg,
                                      (const float2*)table, rotary_dim, (float*)kc, (float*)vc, block_table, bt_width,
                                      page_size, num_pages, nh, nkv, hd, max_pos, err);

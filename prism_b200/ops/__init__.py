@@ -443,7 +443,13 @@ def rope_kv_write_partial(parts: torch.Tensor, bias: Optional[torch.Tensor], q_o
            "rope_kv_write_partial")
 
 
-QKV_FUSED = os.environ.get("PRISM_QKV_FUSED", "1") != "0"
+# The qkv projection of a few tokens.  Default: K-split tcgen05 GEMM -> float32 partial sums -> one kernel that
+# adds them and the bias, rotates and stores (several CTAs per token).  PRISM_QKV_FUSED=1: all of it in the GEMM's
+# epilogue, the K-split CTAs as a cluster (one launch fewer, but the epilogue of 36 clusters is slower than the
+# separate kernel's 64 CTAs: 3.15 against 3.10 ms a step at batch 8).  PRISM_QKV_LIBRARY=1 (with PRISM_QKV_PARTIAL=0):
+# the library product and the rotary kernel, for comparison.
+QKV_FUSED = os.environ.get("PRISM_QKV_FUSED", "0") == "1"
+QKV_LIBRARY = os.environ.get("PRISM_QKV_LIBRARY", "0") == "1"
 
 
 def gemm_tc_qkv(x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], q_out: torch.Tensor,
@@ -508,7 +514,11 @@ def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[
             rope_kv_write_partial(parts, qkv_b, q, ctx.positions, ctx.tok_seg, table, rot.rotary_dim, kc, vc,
                                   cache.block_table, cache.num_pages, ctx.max_positions, nkv, ctx.err)
             return q
-    qkv = linear(x, qkv_w, qkv_b)
+    if QKV_LIBRARY and x.dtype == torch.bfloat16:
+        b = qkv_b if (qkv_b is None or qkv_b.dtype == torch.bfloat16) else qkv_b.to(torch.bfloat16)
+        qkv = torch.nn.functional.linear(x, qkv_w, b)
+    else:
+        qkv = linear(x, qkv_w, qkv_b)
     q = qkv[:, :qs].view(T, nh, hd)
     k = qkv[:, qs:qs + kvs].view(T, nkv, hd)
     v = qkv[:, qs + kvs:].view(T, nkv, hd)
