@@ -110,3 +110,39 @@ def test_cutting_behind_a_backlog(name, dtype):
             torch.mm(big, big)
     got = run_trace(runner, steps, before_step=busy)
     compare_with_plain(name, seqs, got, **TOL[dtype])
+
+
+@pytest.mark.parametrize("which", ["all", "norms"])
+def test_tensors_stored_in_float32_under_the_bf16_engine(which, tmp_path):
+    """A model file whose tensors (all of them, or only the norms' weights and the biases) are stored
+    in float32: the bf16 engine keeps those in float32 and still gives the plain model's logits,
+    mixed steps and reused pages included."""
+    from safetensors.torch import load_file, save_file
+    from prism_b200.engine.runner import ModelRunner
+    from prism_b200.weights.loader import load_model_folder
+    from prism_b200.weights.random_init import write_model_folder
+    from helpers import P
+    name = "D"
+    cfg, seed, ps = TINY[name]
+    d = str(tmp_path / "m")
+    write_model_folder(cfg, seed, d, store_dtype=torch.float32)
+    if which == "norms":
+        t = load_file(d + "/model.safetensors")
+        t = {k: (v if (v.dim() == 1) else v.to(torch.bfloat16)) for k, v in t.items()}
+        assert any(v.dtype == torch.float32 for v in t.values()) and any(v.dtype == torch.bfloat16 for v in t.values())
+        save_file(t, d + "/model.safetensors")
+    pcfg, pt = P.load_folder(d)
+    seqs = sequences(name)
+    steps = trace_mixed(seqs, seed=5)
+    _, model, pool = load_model_folder(d, "cuda:0", torch.bfloat16)
+    kept = {p.dtype for p in pool.tensors.values() if p is not None}
+    assert torch.float32 in kept and (which == "all" or torch.bfloat16 in kept)
+    runner = ModelRunner(model, "cuda:0", torch.bfloat16, ps, trace_budget(steps, ps) // ps, 8)
+    got = run_trace(runner, steps)
+    for rid, seq in seqs.items():
+        ref = P.forward(pcfg, pt, list(seq))
+        scale = float(ref.abs().max())
+        for pos in range(len(seq)):
+            err = float((got[(rid, pos)] - ref[pos]).abs().max())
+            assert err <= TOL["bfloat16"]["atol"] + TOL["bfloat16"]["rtol"] * scale, (rid, pos, err)
+    assert len(got) == sum(len(s) for s in seqs.values())
