@@ -75,6 +75,8 @@ def main(argv=None) -> int:
             if e["id"] not in live:
                 runner.begin_request(e["id"])
                 live.add(e["id"])
+            if not e["tokens"] and not e.get("want"):
+                continue                      # a request that brings no tokens this step: nothing to run
             segs.append(Segment(e["id"], e["tokens"], e.get("want", [])))
         logits = runner.step(segs)
         if logits is not None and logits.shape[0] > 0:
