@@ -129,8 +129,12 @@ def bench_attn_prefill(args):
     kc, vc, bt, q, pos, seg, seg_start, cached, n_pages = paged_case(1, args.cached, Tn)
     out = torch.empty(Tn, NH * HD, device=DEV, dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    kern = ops.attention_prefill_bf16 if args.mma_sync else ops.attention_prefill_tc
-    fn = lambda: kern(q, out, kc, vc, bt, seg_start, cached, Tn, n_pages, None, HD ** -0.5, err)
+    if args.mma_sync:
+        fn = lambda: ops.attention_prefill_bf16(q, out, kc, vc, bt, seg_start, cached, Tn, n_pages, None, HD ** -0.5, err)
+    else:
+        ns = args.splits or ops.prefill_splits(1, Tn, NH, args.cached + Tn, None)     # as the engine chooses
+        fn = lambda: ops.attention_prefill_tc(q, out, kc, vc, bt, seg_start, cached, Tn, n_pages, None, HD ** -0.5, err,
+                                              nsplit=ns)
     if args.once:
         for _ in range(3):
             fn()
@@ -138,7 +142,7 @@ def bench_attn_prefill(args):
         return
     t = timeit(fn)
     fl = 4 * NH * HD * (Tn * (Tn + 1) / 2 + Tn * args.cached)
-    print(f"attn_prefill ({'mma.sync' if args.mma_sync else 'tcgen05'}) T={Tn} cached={args.cached}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s (causal flops)")
+    print(f"attn_prefill ({'mma.sync' if args.mma_sync else f'tcgen05, {ns} split(s)'}) T={Tn} cached={args.cached}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s (causal flops)")
 
 
 def bench_small(args):
@@ -173,7 +177,7 @@ if __name__ == "__main__":
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--bound", type=int, default=0, help="context bound used to choose the splits")
-    ap.add_argument("--splits", type=int, default=0, help="attn_decode: CTAs per (token, kv head); 0 = the engine's choice")
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: CTAs per (token, kv head); attn_prefill: CTAs that share a query tile's keys; 0 = the engine's choice")
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--cached", type=int, default=0, help="attn_prefill: tokens already in the cache before the portion")
     ap.add_argument("--mma-sync", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")

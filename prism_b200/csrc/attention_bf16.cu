@@ -44,3 +44,17 @@ PRISM_EXPORT int prism_attention_prefill_bf16(const void* q, int q_stride, void*
     return hd == 64 ? prism::launch_prefill<64>(ARGS) : prism::launch_prefill<128>(ARGS);
 #undef ARGS
 }
+
+// Merge of split partial results (the decode kernel's, or the tcgen05 prefill kernel's with nsplit > 1):
+// part_o float [T, nh, nsplit, hd] unnormalised outputs, part_ml float [T, nh, nsplit, 2] (reference exponent in
+// log2 units, sum); out bf16 [T, nh * hd] with row stride out_stride.
+PRISM_EXPORT int prism_attention_merge_bf16(const float* part_o, const float* part_ml, int nsplit, void* out,
+                                            int out_stride, int T, int nh, int hd, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (nsplit < 1 || (hd != 64 && hd != 128)) return (int)cudaErrorInvalidValue;
+    if (hd == 64)
+        return (int)prism::launch_kernel(prism::attn_merge_kernel<64>, dim3(T * nh), dim3(64), 0, stream, part_o, part_ml,
+                                         nsplit, (__nv_bfloat16*)out, out_stride, nh);
+    return (int)prism::launch_kernel(prism::attn_merge_kernel<128>, dim3(T * nh), dim3(128), 0, stream, part_o, part_ml,
+                                     nsplit, (__nv_bfloat16*)out, out_stride, nh);
+}

@@ -110,15 +110,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int out_stride,
                        const int* __restrict__ block_table, int bt_width, const int* __restrict__ seg_start,
                        const int* __restrict__ cached_len, int nh, int nkv, int page_size, int num_pages, int window,
-                       float scale_log2, int* err) {
+                       float scale_log2, int* err, int nsplit, float* __restrict__ part_o, float* __restrict__ part_ml) {
     using C = ACfg<HD>;
     pdl_wait();
     // Heads vary fastest, and later query tiles (which see more keys) come first: the longest CTAs of
     // all heads start together and the short ones fill the gaps; the heads of one kv group walk the
     // same keys at the same time, so K and V are read from HBM once.
+    // nsplit > 1 (a short portion against a long cache, too few query tiles to fill the GPU): the key
+    // tiles of a query tile are shared among nsplit CTAs; each leaves (reference, sum, unnormalised
+    // output) per row in part_ml / part_o, laid out as the decode kernel's partials, for the merge kernel.
     const int seg = blockIdx.z, h = blockIdx.x;
     const int s0 = seg_start[seg], qlen = seg_start[seg + 1] - s0;
-    const int q0 = (gridDim.y - 1 - blockIdx.y) * BQ;
+    const int split = blockIdx.y % nsplit;
+    const int q0 = (gridDim.y / nsplit - 1 - blockIdx.y / nsplit) * BQ;
     if (q0 >= qlen) return;
 
     extern __shared__ unsigned char smem_raw[];
@@ -147,7 +151,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int* bt = block_table + (size_t)seg * bt_width;
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;     // first key any row sees
     const int hi = pos0 + rows - 1;                                                   // last key any row sees
-    const int t0 = lo / BK, n = hi / BK + 1 - t0;
+    int t0 = lo / BK, n = hi / BK + 1 - t0;
+    if (nsplit > 1) {
+        const int per = (n + nsplit - 1) / nsplit;
+        t0 += split * per;
+        n = min(per, n - split * per);
+        if (n <= 0) {                 // no key tile for this split: an empty partial
+            for (int i = threadIdx.x; i < rows * HD; i += THREADS)
+                part_o[(((size_t)(tok0 + i / HD) * nh + h) * nsplit + split) * HD + i % HD] = 0.f;
+            for (int r = threadIdx.x; r < rows; r += THREADS) {
+                float* ml = part_ml + (((size_t)(tok0 + r) * nh + h) * nsplit + split) * 2;
+                ml[0] = -INFINITY;
+                ml[1] = 0.f;
+            }
+            return;
+        }
+    }
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -350,7 +369,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // it was issued after the S that this warp just finished with - and such a wait once passed two
         // phases early, about one step in ten under load.)
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0, abortp));
-        if (ok) {
+        if (ok && nsplit > 1) {
+            tc_fence_after();
+            const size_t slot = ((size_t)(tok0 + r) * nh + h) * nsplit + split;
+            float* prow = part_o + slot * HD;
+            if (r < rows) {
+                part_ml[slot * 2] = m_run;
+                part_ml[slot * 2 + 1] = l_run;
+            }
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(lane_base + C::O_COL + c * 32, o);
+                tmem_wait_ld();
+                if (r < rows) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 8; ++v4)
+                        *reinterpret_cast<uint4*>(prow + c * 32 + v4 * 4) =
+                            make_uint4(o[v4 * 4], o[v4 * 4 + 1], o[v4 * 4 + 2], o[v4 * 4 + 3]);
+                }
+            }
+        } else if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* orow = out + (size_t)(tok0 + r) * out_stride + (size_t)h * HD;
@@ -385,7 +424,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch(const void* q, int q_stride, int T, void* out, int out_stride, const void* kc, const void* vc, int cache_pages,
            const int* bt, int bt_width, const int* seg_start, const int* cached_len, int S, int max_q_len, int nh, int nkv,
-           int page_size, int num_pages, int window, float scale, int* err, cudaStream_t stream) {
+           int page_size, int num_pages, int window, float scale, int* err, int nsplit, float* part_o, float* part_ml,
+           cudaStream_t stream) {
     using C = ACfg<HD>;
     CUtensorMap mq, mk, mv;
     int rc = make_map(&mq, q, T, (long long)nh * HD, q_stride, BQ);
@@ -396,10 +436,10 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
     if (rc) return rc;
     auto kern = attn_prefill_tc_kernel<HD>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
-    dim3 grid(nh, (max_q_len + BQ - 1) / BQ, S);
+    dim3 grid(nh, (max_q_len + BQ - 1) / BQ * nsplit, S);
     return (int)launch_kernel(kern, grid, dim3(THREADS), C::SMEM, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride, bt,
                               bt_width, seg_start, cached_len, nh, nkv, page_size, num_pages, window,
-                              scale * 1.4426950408889634f, err);
+                              scale * 1.4426950408889634f, err, nsplit, part_o, part_ml);
 }
 
 }  // namespace tca
@@ -410,20 +450,26 @@ PRISM_EXPORT int prism_attention_prefill_tc_supported(int hd, int nh, int nkv, i
     return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && page_size > 0 && page_size % prism::tca::BK == 0;
 }
 
+// nsplit > 1: the key tiles of every query tile are shared among nsplit CTAs, which leave partial results in
+// part_o (float [T, nh, nsplit, hd]) and part_ml (float [T, nh, nsplit, 2]) for prism_attention_merge_bf16; `out`
+// is then not written here.
 // Prefill / portions: S segments; segment s has tokens seg_start[s] .. seg_start[s+1]-1 of q [T, nh, hd] at positions
 // cached_len[s] + i.  kc / vc: bf16 [cache_pages, page_size, nkv, hd]; block-table entries are < num_pages <= cache_pages.
 PRISM_EXPORT int prism_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* kc,
                                             const void* vc, int cache_pages, const int* block_table, int bt_width,
                                             const int* seg_start, const int* cached_len, int S, int max_q_len, int nh,
                                             int nkv, int hd, int page_size, int num_pages, int window, float scale,
-                                            int* err, cudaStream_t stream) {
+                                            int* err, int nsplit, float* part_o, float* part_ml, cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0 || T <= 0) return 0;
-    if (!prism_attention_prefill_tc_supported(hd, nh, nkv, page_size) || S > 65535 || (max_q_len + prism::tca::BQ - 1) / prism::tca::BQ > 65535 || q_stride % 8 ||
+    if (nsplit < 1 || (nsplit > 1 && (part_o == nullptr || part_ml == nullptr || ((uintptr_t)part_o & 15))))
+        return (int)cudaErrorInvalidValue;
+    if (!prism_attention_prefill_tc_supported(hd, nh, nkv, page_size) || S > 65535 ||
+        (long long)((max_q_len + prism::tca::BQ - 1) / prism::tca::BQ) * nsplit > 65535 || q_stride % 8 ||
         out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
         num_pages > cache_pages || scale <= 0.f)
         return (int)cudaErrorInvalidValue;
 #define ARGS q, q_stride, T, out, out_stride, kc, vc, cache_pages, block_table, bt_width, seg_start, cached_len, S, \
-             max_q_len, nh, nkv, page_size, num_pages, window, scale, err, stream
+             max_q_len, nh, nkv, page_size, num_pages, window, scale, err, nsplit, part_o, part_ml, stream
     return hd == 64 ? prism::tca::launch<64>(ARGS) : prism::tca::launch<128>(ARGS);
 #undef ARGS
 }

@@ -96,7 +96,8 @@ class _Sig:
                                     _f, _p, _p]
     prism_attention_prefill_tc_supported = [_i, _i, _i, _i]
     prism_attention_prefill_tc = [_p, _i, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
-                                  _f, _p, _p]
+                                  _f, _p, _i, _p, _p, _p]
+    prism_attention_merge_bf16 = [_p, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_swiglu = [_p, _p, _i, _i, _i, _p]
     prism_sgemm_nt = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _p]
     prism_sample = [_p, _i, _i, _i, _p, _p, _p, _p]
@@ -657,10 +658,44 @@ def attention_prefill_bf16(q, out, k_cache, v_cache, block_table, seg_start, cac
                                               _stream()), "attention_prefill_bf16")
 
 
+PREFILL_SPLIT_MIN_TILES = 16      # key tiles (of 64) a split CTA should keep
+PREFILL_SPLIT_FROM_TILES = 64     # fewer key tiles than this are not split: the merge costs as much as it saves
+
+
+def prefill_splits(S: int, max_q_len: int, nh: int, max_kv_len: int, window: Optional[int]) -> int:
+    """CTAs that share the key tiles of one (head, 128 query rows) in the tcgen05 prefill kernel: 1 unless
+    the query tiles alone leave most of the GPU idle and the keys are many (a short portion against a
+    long cache); then as many as fill the two CTAs per SM, each with at least PREFILL_SPLIT_MIN_TILES.
+    (Measured at the 7B head counts, 128 new tokens: 2,048 cached 44 us whole and 65 us in 2 splits;
+    8,192 cached 127 -> 46 us in 8; 32,768 cached 471 -> 86 us in 10.)"""
+    if os.environ.get("PRISM_PREFILL_SPLITS"):
+        return int(os.environ["PRISM_PREFILL_SPLITS"])
+    ctas = S * nh * ((max_q_len + 127) // 128)
+    span = min(max_kv_len, window + max_q_len) if window else max_kv_len
+    tiles = (span + 63) // 64
+    if tiles < PREFILL_SPLIT_FROM_TILES:
+        return 1
+    return max(1, min((2 * NUM_SMS) // max(1, ctas), tiles // PREFILL_SPLIT_MIN_TILES, 16))
+
+
+def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor):
+    """``out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)`` over the splits' partial results
+    ``part_o [T, nh, nsplit, hd]`` / ``part_ml [T, nh, nsplit, 2]`` (float32); ``out`` bf16 ``[T, nh * hd]``."""
+    _cuda(part_o, part_ml, out)
+    T, nh, ns, hd = part_o.shape
+    assert part_o.is_contiguous() and part_ml.is_contiguous() and part_ml.shape == (T, nh, ns, 2)
+    assert part_o.dtype == torch.float32 and part_ml.dtype == torch.float32 and out.dtype == torch.bfloat16
+    assert out.stride(1) == 1 and out.shape == (T, nh * hd)
+    _check(lib().prism_attention_merge_bf16(_ptr(part_o), _ptr(part_ml), ns, _ptr(out), out.stride(0), T, nh, hd,
+                                            _stream()), "attention_merge")
+
+
 def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seg_start, cached_len, max_q_len,
-                         num_pages, window, scale, err):
+                         num_pages, window, scale, err, nsplit: int = 1, first_token: int = 0):
     """The same on the 5th-generation tensor cores (tcgen05, TMA, tensor memory): 128 query
-    rows per CTA.  Head size 64 or 128, pages of a multiple of 64 tokens."""
+    rows per CTA.  Head size 64 or 128, pages of a multiple of 64 tokens.  ``nsplit`` > 1: that many
+    CTAs share a query tile's keys and a second kernel merges their partial results (of the tokens
+    from ``first_token`` on: the segments given must cover exactly those)."""
     _cuda(q, out, k_cache, v_cache, block_table, seg_start, cached_len)
     T, nh, hd = q.shape
     nkv, P = k_cache.shape[2], k_cache.shape[1]
@@ -668,11 +703,17 @@ def attention_prefill_tc(q, out, k_cache, v_cache, block_table, seg_start, cache
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1 and seg_start.shape[0] == S + 1
     assert k_cache.is_contiguous() and v_cache.is_contiguous() and v_cache.shape == k_cache.shape
+    po = pml = None
+    if nsplit > 1:
+        po = torch.empty((T, nh, nsplit, hd), dtype=torch.float32, device=q.device)
+        pml = torch.empty((T, nh, nsplit, 2), dtype=torch.float32, device=q.device)
     _check(lib().prism_attention_prefill_tc(_ptr(q), q.stride(0), T, _ptr(out), out.stride(0), _ptr(k_cache),
                                             _ptr(v_cache), k_cache.shape[0], _ptr(block_table), block_table.shape[1],
                                             _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, hd,
-                                            P, num_pages, int(window or 0), float(scale), _ptr(err),
-                                            _stream()), "attention_prefill_tc")
+                                            P, num_pages, int(window or 0), float(scale), _ptr(err), int(nsplit),
+                                            _ptr(po), _ptr(pml), _stream()), "attention_prefill_tc")
+    if nsplit > 1:
+        attention_merge(po[first_token:], pml[first_token:], out[first_token:])
 
 
 def attention_prefill_tc_supported(hd: int, nh: int, nkv: int, page_size: int) -> bool:
@@ -731,8 +772,9 @@ def _attention_portions(ctx, q, out, cache, window, scale, first_seg: int):
     seg_start, cached_len, bt = ctx.seg_start[first_seg:], ctx.cached_len[first_seg:], cache.block_table[first_seg:]
     if (ATTENTION_TC and ctx.max_q_len >= ATTENTION_TC_MIN_Q and scale > 0 and cache.k.is_contiguous()
             and cache.v.is_contiguous() and attention_prefill_tc_supported(hd, nh, nkv, cache.k.shape[1])):
+        ns = prefill_splits(cached_len.shape[0], ctx.max_q_len, nh, ctx.max_kv_len, window)
         attention_prefill_tc(q, out, cache.k, cache.v, bt, seg_start, cached_len, ctx.max_q_len, cache.num_pages,
-                             window, scale, ctx.err)
+                             window, scale, ctx.err, nsplit=ns, first_token=first_seg)
     else:
         attention_prefill_bf16(q, out, cache.k, cache.v, bt, seg_start, cached_len, ctx.max_q_len, cache.num_pages,
                                window, scale, ctx.err)

@@ -159,14 +159,15 @@ def test_decode_graph_replay_gives_the_eager_logits(size):
 
 def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypatch):
     """6,000 tokens (too long for the plain model on the CPU): the tcgen05 prefill attention and the
-    split-KV decode attention against the shape-generic kernel, which shares no code with them, whole
-    and in portions of 1,024, followed by a few decode steps through graphs."""
+    split-KV decode attention against the shape-generic kernel, which shares no code with them, whole,
+    in portions of 1,024, and with a tail of short portions behind a long cache (whose key tiles several
+    CTAs share, with a merge after them), followed by a few decode steps through graphs."""
     from prism_b200 import Engine, EngineConfig, ops
     from prism_b200.engine.batch import Segment
     cfg = dict(SHAPE_7B, vocab_size=152064)
     prompt = random_tokens(150000, 6000, 4)
     logits = {}
-    for mode in ("fast", "generic", "portions"):
+    for mode in ("fast", "generic", "portions", "short_portions"):
         monkeypatch.setattr(ops, "FORCE_GENERIC_ATTENTION", mode == "generic")
         eng = Engine(None, EngineConfig(kv_page_size=256, num_pages=32, max_seq_len=8192, use_cuda_graph=mode != "generic"),
                      dtype="bfloat16", config=cfg, random_seed=0)
@@ -176,6 +177,11 @@ def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypat
             for c in range(0, 6000, 1024):
                 part = prompt[c:c + 1024]
                 lg = r.step([Segment(0, part, [len(part) - 1])])
+        elif mode == "short_portions":
+            assert ops.prefill_splits(1, 152, cfg["num_attention_heads"], 4936 + 152, None) > 1
+            r.step([Segment(0, prompt[:4936], [])])
+            for c in range(4936, 6000, 152):
+                lg = r.step([Segment(0, prompt[c:c + 152], [151])])
         else:
             lg = r.step([Segment(0, prompt, [5999])])
         outs = [lg.float().cpu()] + [r.step([Segment(0, [100 + s], [0])]).float().cpu() for s in range(4)]
@@ -183,6 +189,6 @@ def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypat
         logits[mode] = outs
         del eng, r
     scale = float(logits["fast"][0].abs().max())
-    for mode in ("generic", "portions"):
+    for mode in ("generic", "portions", "short_portions"):
         for a, b in zip(logits["fast"], logits[mode]):
             assert float((a - b).abs().max()) <= 0.03 * scale, (mode, float((a - b).abs().max()), scale)

@@ -553,9 +553,12 @@ PREFILL_TC_CASES = [
 ]
 
 
+@pytest.mark.parametrize("nsplit", [1, 2, 5, 16])
 @pytest.mark.parametrize("case", PREFILL_TC_CASES)
-def test_attention_prefill_tc(case):
-    """The tcgen05 kernel: 128-row query tiles, keys by TMA through the block table."""
+def test_attention_prefill_tc(case, nsplit):
+    """The tcgen05 kernel: 128-row query tiles, keys by TMA through the block table.  With nsplit > 1 the
+    key tiles of a query tile are shared among that many CTAs and merged afterwards; with more splits than
+    key tiles some CTAs leave an empty partial result, and a split may hold only keys that a row cannot see."""
     ops = _ops()
     nh, nkv, hd, P, window, segs = case
     c = PagedCase(segs, nh, nkv, hd, P, torch.bfloat16, seed=24)
@@ -567,9 +570,38 @@ def test_attention_prefill_tc(case):
     for _ in range(2):
         out.fill_(float("nan"))
         ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
-                                 window, scale, err)
+                                 window, scale, err, nsplit=nsplit)
         assert int(err) == 0 and not torch.isnan(out.float()).any()
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+
+
+def test_attention_prefill_tc_split_after_decode_tokens():
+    """Split portions behind single decoded tokens in one batch, as a step has them: the kernel gets the
+    segments from ``first`` on, indexes the partial results by the token's place in the whole batch, and the
+    merge writes only the portions' rows."""
+    ops = _ops()
+    nh, nkv, hd, P, first = 8, 2, 128, 64, 3
+    c = PagedCase([(70, 1), (0, 1), (900, 1), (2000, 140), (500, 33)], nh, nkv, hd, P, torch.bfloat16, seed=26)
+    scale = hd ** -0.5
+    ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, None, scale)
+    out = torch.full((c.T, nh * hd), 9.0, dtype=torch.bfloat16, device=DEV)
+    err = _err()
+    ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt[first:], c.seg_start[first:], c.cached_len[first:], 140,
+                             c.num_pages, None, scale, err, nsplit=4, first_token=first)
+    assert int(err) == 0
+    assert torch.equal(out[:first].float(), torch.full_like(out[:first].float(), 9.0))      # not this call's rows
+    assert torch.allclose(out[first:].float(), ref[first:], atol=2e-2, rtol=2e-2)
+
+
+def test_prefill_splits_choice():
+    """Splits only when the query tiles leave the GPU idle and the keys are many."""
+    ops = _ops()
+    assert ops.prefill_splits(1, 2048, 28, 2048, None) == 1          # 448 CTAs already
+    assert ops.prefill_splits(1, 128, 28, 640, None) == 1            # 10 key tiles: not worth a merge
+    n = ops.prefill_splits(1, 128, 28, 32768 + 128, None)
+    assert 2 <= n <= 16 and 28 * n <= 2 * ops.NUM_SMS
+    assert ops.prefill_splits(1, 128, 28, 32768 + 128, 512) == 1     # a window of 512 keys: few tiles
+    assert ops.prefill_splits(4, 256, 28, 32768, None) == 1
 
 
 def test_attention_prefill_tc_is_reproducible():
@@ -608,13 +640,13 @@ def test_attention_prefill_tc_refuses():
                                  c.seg_start, c.cached_len, c.max_q, c.num_pages, None, 1.0, _err())
 
 
-@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill", "prefill_tc"])
+@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill", "prefill_tc", "prefill_tc_split"])
 def test_attention_finds_one_far_key(kind):
     """One key among thousands carries the whole softmax: the query and that
     key are scaled so that its score stands out, and its value is marked.  A
     kernel that drops a tile, a split or a page loses the mark."""
     ops = _ops()
-    nh, nkv, hd, P = 8, 2, 64, (64 if kind == "prefill_tc" else 16)
+    nh, nkv, hd, P = 8, 2, 64, (64 if kind.startswith("prefill_tc") else 16)
     dtype = torch.float32 if kind == "generic32" else torch.bfloat16
     ctx = 3000
     segs = [(ctx, 1)] if not kind.startswith("prefill") else [(ctx - 40, 41)]
@@ -634,9 +666,9 @@ def test_attention_finds_one_far_key(kind):
             ns = 9
             ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, None, scale, ns,
                                       torch.empty(c.T, nh, ns, hd, device=DEV), torch.empty(c.T, nh, ns, 2, device=DEV), err)
-        elif kind == "prefill_tc":
+        elif kind.startswith("prefill_tc"):
             ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
-                                     None, scale, err)
+                                     None, scale, err, nsplit=7 if kind.endswith("split") else 1)
         else:
             ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
                                        None, scale, err)
@@ -644,13 +676,13 @@ def test_attention_finds_one_far_key(kind):
         assert torch.allclose(out[-1].float(), torch.full_like(out[-1].float(), 5.0), atol=0.05), (kind, far, out[-1][:4])
 
 
-@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill", "prefill_tc"])
+@pytest.mark.parametrize("kind", ["generic32", "generic16", "decode", "prefill", "prefill_tc", "prefill_tc_split"])
 def test_attention_window_edge(kind):
     """A sliding window's edge, made visible: the key just outside the window
     carries an enormous score and a marked value and must not be seen; the key
     just inside must be (move the mark there and it dominates)."""
     ops = _ops()
-    nh, nkv, hd, P, window = 4, 2, 64, (64 if kind == "prefill_tc" else 16), 37
+    nh, nkv, hd, P, window = 4, 2, 64, (64 if kind.startswith("prefill_tc") else 16), 37
     dtype = torch.float32 if kind == "generic32" else torch.bfloat16
     for ctx in (36, 37, 64, 100, 129, 500):                        # the query sits at position ctx
         segs = [(ctx, 1)] if not kind.startswith("prefill") else [(max(0, ctx - 5), ctx - max(0, ctx - 5) + 1)]
@@ -673,9 +705,9 @@ def test_attention_window_edge(kind):
                 ns = 3
                 ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, ns,
                                           torch.empty(c.T, nh, ns, hd, device=DEV), torch.empty(c.T, nh, ns, 2, device=DEV), err)
-            elif kind == "prefill_tc":
+            elif kind.startswith("prefill_tc"):
                 ops.attention_prefill_tc(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
-                                         window, scale, err)
+                                         window, scale, err, nsplit=3 if kind.endswith("split") else 1)
             else:
                 ops.attention_prefill_bf16(c.q, out, c.k, c.v, c.bt, c.seg_start, c.cached_len, c.max_q, c.num_pages,
                                            window, scale, err)
