@@ -29,6 +29,40 @@ PRISM_EXPORT int prism_attention_decode_bf16(const void* q, int q_stride, void* 
 #undef ARGS
 }
 
+// Decode with the back half of the qkv projection inside: instead of q and a cache that already holds the tokens'
+// own keys and values, the kernel gets the projection's float32 partial sums parts [ks, T, D] (D = (nh + 2 nkv) * hd,
+// q | k | v), the bias [D] (float or bf16, or null) and the step's rotary table [T, hd / 2] of (cos, sin) pairs; it
+// adds, biases and rotates (all of hd) itself and stores each token's key and value at its position.
+PRISM_EXPORT int prism_attention_decode_qkv_bf16(const float* parts, int ks, const void* bias, int bias_dtype,
+                                                 const void* table, int max_pos, void* out, int out_stride, void* kc,
+                                                 void* vc, const int* block_table, int bt_width, const int* positions,
+                                                 const int* tok_seg, int T, int nh, int nkv, int hd, int page_size,
+                                                 int num_pages, int window, float scale, float* part_o, float* part_ml,
+                                                 int nsplit, int* counters, int* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535 || ks < 1 ||
+        parts == nullptr || table == nullptr || ((uintptr_t)parts & 15) || ((uintptr_t)table & 15) ||
+        ((uintptr_t)bias & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
+        (bias_dtype != PRISM_DTYPE_F32 && bias_dtype != PRISM_DTYPE_BF16) || (counters != nullptr && nsplit > 64))
+        return (int)cudaErrorInvalidValue;
+    prism::DecodeQKV f;
+    f.D = (nh + 2 * nkv) * hd;
+    f.parts = parts;
+    f.part_stride = (size_t)T * f.D;
+    f.ks = ks;
+    f.bias = bias;
+    f.bias_bf16 = bias_dtype == PRISM_DTYPE_BF16;
+    f.table = (const float2*)table;
+    f.kc = (__nv_bfloat16*)kc;
+    f.vc = (__nv_bfloat16*)vc;
+    f.max_pos = max_pos;
+#define ARGS (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
+             (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
+             window, scale, part_o, part_ml, nsplit, err, stream, counters, false, &f
+    return hd == 64 ? prism::launch_decode<64>(ARGS) : prism::launch_decode<128>(ARGS);
+#undef ARGS
+}
+
 // Prefill / mixed: S segments; segment s has tokens seg_start[s] .. seg_start[s+1]-1 at positions cached_len[s] + i.
 PRISM_EXPORT int prism_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
                                               const void* kc, const void* vc, const int* block_table,

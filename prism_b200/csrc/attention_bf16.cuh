@@ -50,7 +50,66 @@ __device__ __forceinline__ float exp2_fast(float x, float m) {
 // CLUSTER: the CTAs of one (token, kv head) - one per split - form a thread-block cluster and merge
 // their partial results through distributed shared memory: no partials in global memory, no second
 // kernel.  At most 8 splits (the portable cluster size).
-template <int HD, bool CLUSTER>
+//
+// FUSED: the kernel takes over the back half of the qkv projection.  The projection of a few tokens
+// leaves float32 partial sums [ks, T, D] (D = (nh + 2 nkv) * HD, q | k | v); every CTA adds up, biases
+// and rotates the query rows of its kv head itself, and the CTA whose keys end at the token's own
+// position does the same for that token's key and value, stores them in the cache and puts them into
+// its tile in shared memory.  One kernel and one grid boundary fewer in the decode step; nothing of
+// the cache depends on the kernels before this one any more, so all tiles are requested ahead of the wait.
+struct DecodeQKV {
+    const float* parts;        // [ks, T, D] partial sums of the qkv projection
+    size_t part_stride;        // T * D
+    int ks, D;
+    const void* bias;          // [D] or null
+    int bias_bf16;
+    const float2* table;       // [T, HD / 2] (cos, sin) of the step's positions
+    __nv_bfloat16* kc;         // the cache planes, writable
+    __nv_bfloat16* vc;
+    int max_pos;
+};
+
+// 4 consecutive sums: bias + partial sums in the order s = 0, 1, ... (as rope_kv_partial_kernel adds them)
+__device__ __forceinline__ void qkv_sum4(const DecodeQKV& f, const float* parts, int t, size_t col, float (&v)[4]) {
+    if (f.bias != nullptr) {
+        if (f.bias_bf16) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(f.bias) + col);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(f.bias) + col);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        }
+    } else {
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+    }
+    const float* p0 = parts + (size_t)t * f.D + col;
+    for (int s0 = 0; s0 < f.ks; s0 += 4) {
+        float4 p[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (s0 + u < f.ks) p[u] = *reinterpret_cast<const float4*>(p0 + (size_t)(s0 + u) * f.part_stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (s0 + u < f.ks) { v[0] += p[u].x; v[1] += p[u].y; v[2] += p[u].z; v[3] += p[u].w; }
+    }
+}
+// rotate the pairs (x1[e], x2[e]) by the angles tab[e] and round: 4 + 4 bf16
+__device__ __forceinline__ void rotate4(const float (&x1)[4], const float (&x2)[4], const float2* tab, uint2& lo, uint2& hi) {
+    const float4 t01 = reinterpret_cast<const float4*>(tab)[0], t23 = reinterpret_cast<const float4*>(tab)[1];
+    const float c[4] = {t01.x, t01.z, t23.x, t23.z}, sn[4] = {t01.y, t01.w, t23.y, t23.w};
+    float y1[4], y2[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        y1[e] = x1[e] * c[e] - x2[e] * sn[e];
+        y2[e] = x2[e] * c[e] + x1[e] * sn[e];
+    }
+    lo = make_uint2(pack_bf16(y1[0], y1[1]), pack_bf16(y1[2], y1[3]));
+    hi = make_uint2(pack_bf16(y2[0], y2[1]), pack_bf16(y2[2], y2[3]));
+}
+
+template <int HD, bool CLUSTER, bool FUSED = false>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
@@ -58,8 +117,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh,
                    int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit,
-                   __nv_bfloat16* __restrict__ out, int out_stride, int* __restrict__ counters, int* err) {
+                   __nv_bfloat16* __restrict__ out, int out_stride, int* __restrict__ counters, int* err,
+                   const DecodeQKV fq) {
     __shared__ int s_last;
+    __shared__ __align__(16) __nv_bfloat16 s_own_kv[FUSED ? 2 * HD : 8];     // FUSED: this step's own key and value
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int SUB_ELEMS = 16 * STRIDE;                           // one warp's 16 keys of a tile
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -142,7 +203,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int own_tile = hi / ATT_TILE;
     bool waited = false;
     auto load_tile = [&](int tile, int stage) {
-        if (tile == own_tile && !waited) {
+        if (!FUSED && tile == own_tile && !waited) {
             pdl_wait();
             waited = true;
         }
@@ -163,12 +224,68 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     // Q rows of this kv head's group (rows >= g are zero), with plain loads: visible after the
     // first barrier of the loop below
-    const __nv_bfloat16* q_now = pdl_fresh(q);       // q is the previous kernel's output
-    for (int i = tid; i < 16 * (HD / 8); i += ATT_THREADS) {
-        const int r = i / (HD / 8), c = i % (HD / 8);
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < g) v = *reinterpret_cast<const uint4*>(q_now + (size_t)t * q_stride + ((size_t)kvh * g + r) * HD + c * 8);
-        *reinterpret_cast<uint4*>(Qs + r * STRIDE + c * 8) = v;
+    // FUSED: this CTA holds the token's own position as its last key
+    const bool owner = FUSED && t0 < t1 && t1 == own_tile + 1;
+    if (FUSED) {
+        constexpr int HALF = HD / 2;
+        const float* parts = pdl_fresh(fq.parts);            // the projection's partial sums and the step's angles:
+        const float2* tab = pdl_fresh(fq.table) + (size_t)t * HALF;      // outputs of kernels before this one
+        for (int i = tid; i < (16 - g) * (HD / 8); i += ATT_THREADS)
+            *reinterpret_cast<uint4*>(Qs + (g + i / (HD / 8)) * STRIDE + (i % (HD / 8)) * 8) = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = tid; i < g * (HALF / 4); i += ATT_THREADS) {
+            const int r = i / (HALF / 4), j = (i % (HALF / 4)) * 4;
+            const size_t col = ((size_t)kvh * g + r) * HD + j;
+            float x1[4], x2[4];
+            qkv_sum4(fq, parts, t, col, x1);
+            qkv_sum4(fq, parts, t, col + HALF, x2);
+            uint2 a, b;
+            rotate4(x1, x2, tab + j, a, b);
+            *reinterpret_cast<uint2*>(Qs + r * STRIDE + j) = a;
+            *reinterpret_cast<uint2*>(Qs + r * STRIDE + j + HALF) = b;
+        }
+        if (owner) {
+            // the token's own key (rotated) and value: into the cache for later steps, and into shared
+            // memory for this one
+            const bool pos_ok = pos >= 0 && pos < fq.max_pos;
+            const int page = pos_ok ? bt[page_shift >= 0 ? pos >> page_shift : pos / page_size] : -1;
+            const bool store = pos_ok && page >= 0 && page < num_pages;
+            if (!store && tid == 0) report_error(err, pos_ok ? PRISM_ERR_PAGE_RANGE : PRISM_ERR_POSITION_RANGE);
+            const int in_page = pos_ok ? (page_shift >= 0 ? pos & (page_size - 1) : pos % page_size) : 0;
+            const size_t slot = store ? ((size_t)page * page_size + in_page) * (size_t)nkv * HD + (size_t)kvh * HD : 0;
+            for (int i = tid; i < HALF / 4 + HD / 4; i += ATT_THREADS) {
+                if (i < HALF / 4) {
+                    const int j = i * 4;
+                    const size_t col = (size_t)nh * HD + (size_t)kvh * HD + j;
+                    float x1[4], x2[4];
+                    qkv_sum4(fq, parts, t, col, x1);
+                    qkv_sum4(fq, parts, t, col + HALF, x2);
+                    uint2 a, b;
+                    rotate4(x1, x2, tab + j, a, b);
+                    *reinterpret_cast<uint2*>(s_own_kv + j) = a;
+                    *reinterpret_cast<uint2*>(s_own_kv + j + HALF) = b;
+                    if (store) {
+                        *reinterpret_cast<uint2*>(fq.kc + slot + j) = a;
+                        *reinterpret_cast<uint2*>(fq.kc + slot + j + HALF) = b;
+                    }
+                } else {
+                    const int d = (i - HALF / 4) * 4;
+                    const size_t col = (size_t)(nh + nkv) * HD + (size_t)kvh * HD + d;
+                    float x[4];
+                    qkv_sum4(fq, parts, t, col, x);
+                    const uint2 a = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+                    *reinterpret_cast<uint2*>(s_own_kv + HD + d) = a;
+                    if (store) *reinterpret_cast<uint2*>(fq.vc + slot + d) = a;
+                }
+            }
+        }
+    } else {
+        const __nv_bfloat16* q_now = pdl_fresh(q);       // q is the previous kernel's output
+        for (int i = tid; i < 16 * (HD / 8); i += ATT_THREADS) {
+            const int r = i / (HD / 8), c = i % (HD / 8);
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < g) v = *reinterpret_cast<const uint4*>(q_now + (size_t)t * q_stride + ((size_t)kvh * g + r) * HD + c * 8);
+            *reinterpret_cast<uint4*>(Qs + r * STRIDE + c * 8) = v;
+        }
     }
     __syncthreads();
 
@@ -190,6 +307,17 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         __syncwarp();
         const __nv_bfloat16* Ks = KV + ((size_t)(warp * DEC_STAGES + it % DEC_STAGES) * 2) * SUB_ELEMS;
         const __nv_bfloat16* Vs = Ks + SUB_ELEMS;
+        if (FUSED && owner && tile == own_tile && warp == ((pos & (ATT_TILE - 1)) >> 4)) {
+            // the row of the token's own position: what the cache gave for it is stale, the computed
+            // key and value take its place
+            __nv_bfloat16* krow = KV + ((size_t)(warp * DEC_STAGES + it % DEC_STAGES) * 2) * SUB_ELEMS + (pos & 15) * STRIDE;
+            for (int c = lane; c < 2 * (HD / 8); c += 32) {
+                const int which = c / (HD / 8), cc = c % (HD / 8);
+                *reinterpret_cast<uint4*>(krow + which * SUB_ELEMS + cc * 8) =
+                    *reinterpret_cast<const uint4*>(s_own_kv + which * HD + cc * 8);
+            }
+            __syncwarp();
+        }
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};     // odd k-steps: two shorter MMA chains
 #pragma unroll
@@ -570,7 +698,8 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
                   const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
                   int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
-                  int* err, cudaStream_t stream, int* counters = nullptr, bool use_cluster = false) {
+                  int* err, cudaStream_t stream, int* counters = nullptr, bool use_cluster = false,
+                  const DecodeQKV* fused = nullptr) {
     static_assert(dec_smem<HD>() >= (size_t)(5 * 16 * HD + 128 + 32) * sizeof(float) + 16 * TileRow<HD>::STRIDE * 2, "merge scratch must fit");
     dim3 grid(nsplit, nkv, T);
     if (counters == nullptr && use_cluster && nsplit >= 2 && nsplit <= 8) {
@@ -592,13 +721,14 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
         return (int)cudaLaunchKernelEx(&cfg, kc_, q, q_stride, kc, vc, bt, bt_width, positions, tok_seg, nh, nkv, page_size,
                                        page_shift_of(page_size), num_pages, window, scale * 1.4426950408889634f, part_o,
-                                       part_ml, nsplit, out, out_stride, (int*)nullptr, err);
+                                       part_ml, nsplit, out, out_stride, (int*)nullptr, err, DecodeQKV());
     }
-    auto kern = attn_decode_kernel<HD, false>;
+    auto kern = fused != nullptr ? attn_decode_kernel<HD, false, true> : attn_decode_kernel<HD, false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
     cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
                                    positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
-                                   scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, counters, err);
+                                   scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, counters, err,
+                                   fused != nullptr ? *fused : DecodeQKV());
     if (rc != cudaSuccess || counters != nullptr || nsplit == 1) return (int)rc;
     return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD >= 128 ? 128 : 64), 0, stream,
                               (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);

@@ -92,6 +92,8 @@ class _Sig:
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
                                    _p, _p, _i, _p, _i, _p, _p]
+    prism_attention_decode_qkv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
+                                       _i, _f, _p, _p, _i, _p, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
     prism_attention_prefill_tc_supported = [_i, _i, _i, _i]
@@ -641,6 +643,36 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
         launch_count += 1          # the merge kernel
 
 
+def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache, block_table, positions, tok_seg,
+                              num_pages, nh, window, scale, nsplit, part_o, part_ml, err,
+                              fused_merge: Optional[bool] = None):
+    """Decode attention that finishes the qkv projection itself: ``parts [ks, T, (nh + 2 nkv) * hd]`` are the
+    projection's float32 partial sums, ``bias`` its bias or None, ``table [T, hd / 2, 2]`` the step's cos/sin.
+    Every CTA adds, biases and rotates the query rows it needs; the CTA that holds a token's own position
+    does the same for the token's key and value, stores them in the cache and uses them.  The whole head is
+    rotated (rotary_dim == hd)."""
+    _cuda(parts, bias, table, out, k_cache, v_cache, block_table, positions, tok_seg, part_o, part_ml)
+    ks, T, D = parts.shape
+    nkv, P, hd = k_cache.shape[2], k_cache.shape[1], k_cache.shape[3]
+    assert parts.dtype == torch.float32 and parts.is_contiguous() and D == (nh + 2 * nkv) * hd
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.shape == (T, hd // 2, 2)
+    assert k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (T, nh * hd)
+    assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
+    assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
+    fused_merge = FUSED_MERGE if fused_merge is None else fused_merge
+    _check(lib().prism_attention_decode_qkv_bf16(_ptr(parts), ks, _ptr(bias), F32 if bias is None else _dt(bias),
+                                                 _ptr(table), int(max_pos), _ptr(out), out.stride(0), _ptr(k_cache),
+                                                 _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+                                                 _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
+                                                 int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
+                                                 int(nsplit), _ptr(_decode_counters(out.device, T * nkv)) if fused_merge else None,
+                                                 _ptr(err), _stream()), "attention_decode_qkv_bf16")
+    if not fused_merge and nsplit > 1:
+        global launch_count
+        launch_count += 1          # the merge kernel
+
+
 def attention_prefill_bf16(q, out, k_cache, v_cache, block_table, seg_start, cached_len, max_q_len,
                            num_pages, window, scale, err):
     """Tensor-core attention for segments of any length (portions of prompts,
@@ -804,6 +836,46 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
         return
     attention_generic(q, out, cache.k, cache.v, cache.block_table, ctx.positions, ctx.tok_seg,
                       cache.num_pages, window, scale, ctx.err)
+
+
+# PRISM_QKV_IN_ATTENTION=1: in a pure decode step the qkv projection's partial sums go straight to the decode
+# attention kernel, which adds, biases, rotates and stores (no kernel between the projection and attention).
+# Off by default: one launch fewer, the same step time (3.08 ms both ways at batch 8).  The attention CTAs then
+# become resident beside the projection's CTAs, of which only one fits per SM next to them, so half of them start
+# after the projection has ended and ask for their keys only then; with the small rotary kernel in between all of
+# them are resident and have their first tiles on the way before they are released.
+QKV_IN_ATTENTION = os.environ.get("PRISM_QKV_IN_ATTENTION", "0") == "1"
+
+
+def qkv_attention(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], nh: int, nkv: int, hd: int,
+                  rot, cache, window: Optional[int], scale: float, out: torch.Tensor):
+    """An attention layer between its input and its output projection: qkv projection (+ bias), rotary
+    encoding of q and k, store of k and v, attention over the cache plane into ``out [T, nh * hd]``.
+    ``qkv_rotate_store`` followed by ``attention``; with ``QKV_IN_ATTENTION`` a pure decode step of a few
+    tokens runs as two kernels (K-split projection, attention that finishes the projection)."""
+    T = x.shape[0]
+    if (QKV_IN_ATTENTION and QKV_PARTIAL and not QKV_FUSED and ctx.decode_only and cache.write and rot is not None
+            and rot.rotary_dim == hd and x.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+            and not FORCE_GENERIC_ATTENTION and not CLUSTER_MERGE and tc_gemm_ok(x, qkv_w)
+            and cache.k.is_contiguous() and cache.v.is_contiguous() and attention_bf16_supported(hd, nh, nkv)):
+        ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
+        if ks > 1:
+            key = ("rotary_table", rot.inv_freq.data_ptr())          # one table per step for all layers
+            table = ctx.scratch.get(key)
+            if table is None:
+                table = ctx.scratch[key] = ctx.alloc((T, hd // 2, 2), torch.float32)
+                rope_table(ctx.positions, rot.inv_freq, table)
+            parts = ctx.alloc((ks, T, (nh + 2 * nkv) * hd), torch.float32)
+            gemm_tc(x, qkv_w, None, parts, EPI_PARTIAL, ksplit=ks)
+            nsplit = decode_splits(T, nkv, ctx.max_kv_len, window)
+            part_o = ctx.alloc((T, nh, nsplit, hd), torch.float32)
+            part_ml = ctx.alloc((T, nh, nsplit, 2), torch.float32)
+            attention_decode_qkv_bf16(parts, qkv_b, table, ctx.max_positions, out, cache.k, cache.v, cache.block_table,
+                                      ctx.positions, ctx.tok_seg, cache.num_pages, nh, window, scale, nsplit,
+                                      part_o, part_ml, ctx.err)
+            return
+    q = qkv_rotate_store(ctx, x, qkv_w, qkv_b, nh, nkv, hd, rot, cache)
+    attention(ctx, q, out, cache, window, scale)
 
 
 def feed_forward_swiglu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: torch.Tensor):

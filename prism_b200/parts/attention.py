@@ -65,7 +65,10 @@ class GQAAttention(Mixer):
                               cache.k if cache.write else None, cache.v if cache.write else None,
                               cache.block_table, cache.num_pages, ctx.max_positions, ctx.err)
         else:
-            q = ops.qkv_rotate_store(ctx, x, self.w["qkv_w"], self.w.get("qkv_b"), self.nh, self.nkv, self.hd, rot, cache)
+            attn = ctx.alloc((T, qs), x.dtype)
+            ops.qkv_attention(ctx, x, self.w["qkv_w"], self.w.get("qkv_b"), self.nh, self.nkv, self.hd, rot, cache,
+                              self.window, self.scale, attn)
+            return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))
         attn = ctx.alloc((T, qs), x.dtype)
         ops.attention(ctx, q, attn, cache, self.window, self.scale)
         return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))

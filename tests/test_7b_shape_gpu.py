@@ -5,6 +5,8 @@ on the CPU: the production kernels (tensor-core attention, the tcgen05 GEMM
 with its fused epilogues, the library GEMM for long portions) at the sizes
 they were written for, in float32 and bfloat16, whole and cut (GPU)."""
 
+import json
+import os
 import tempfile
 
 import pytest
@@ -86,6 +88,33 @@ def test_7b_sized_layers_with_pages_of_256(folder_and_plain, graphs):
     steps = trace_tail(seqs, 10)
     runner = runner_for(folder, "bfloat16", trace_budget(steps, 256) // 256, page_size=256, graphs=graphs)
     got = run_trace(runner, steps)
+    for rid, seq in seqs.items():
+        scale = float(ref[rid].abs().max())
+        for pos in range(len(seq)):
+            err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
+            assert err <= 5e-3 + 4e-2 * scale, (rid, pos, err, scale)
+    assert runner.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("mode", ["tail", "tail_graphs", "mixed_graphs"])
+def test_7b_sized_layers_with_the_projection_finished_inside_decode_attention(folder_and_plain, mode, monkeypatch):
+    """The optional decode path without a kernel between the qkv projection and attention
+    (``ops.QKV_IN_ATTENTION``): the decode kernel adds the projection's partial sums, rotates, and
+    stores each token's key and value itself."""
+    from prism_b200 import ops
+    monkeypatch.setattr(ops, "QKV_IN_ATTENTION", True)
+    launches = []
+    real = ops.attention_decode_qkv_bf16
+    monkeypatch.setattr(ops, "attention_decode_qkv_bf16", lambda *a, **k: (launches.append(1), real(*a, **k))[1])
+    folder, seqs, ref = folder_and_plain
+    kind = mode.split("_")[0]
+    steps = {"tail": lambda s: trace_tail(s, 12), "mixed": lambda s: trace_mixed(s, seed=5)}[kind](seqs)
+    runner = runner_for(folder, "bfloat16", trace_budget(steps, 64) // 64, graphs=mode.endswith("_graphs"))
+    got = run_trace(runner, steps)
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    qkv_rows = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    if ops.tc_ksplit(qkv_rows, cfg["hidden_size"]) > 1:          # a projection that is not K-split keeps the usual path
+        assert launches, "the fused path did not run"
     for rid, seq in seqs.items():
         scale = float(ref[rid].abs().max())
         for pos in range(len(seq)):

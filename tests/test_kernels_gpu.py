@@ -517,6 +517,66 @@ def test_attention_decode_bf16(case, fused_merge):
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
+@pytest.mark.parametrize("case", DECODE_CASES + [(8, 2, 64, 16, 40, [100, 39, 40, 41, 0], 3)])
+@pytest.mark.parametrize("merge", ["last_cta", "kernel"])
+@pytest.mark.parametrize("bias_dtype", [None, torch.bfloat16, torch.float32])
+def test_attention_decode_finishes_the_qkv_projection(case, merge, bias_dtype):
+    """The decode kernel given the projection's partial sums instead of q and a filled cache: the same output
+    and the same cache contents as the rotary + store kernel followed by the plain decode kernel.  The
+    tokens' own cache rows hold NaN beforehand: they must be computed, not read."""
+    ops = _ops()
+    nh, nkv, hd, P, window, ctxs, nsplit = case
+    c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=27)
+    T, ks, D = c.T, 3, (nh + 2 * nkv) * hd
+    parts = _rand((ks, T, D), torch.float32, 60, scale=0.5)
+    bias = None if bias_dtype is None else _rand((D,), bias_dtype, 61, scale=0.5)
+    inv = (1.0 / (1e4 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).to(DEV)
+    table = torch.empty(T, hd // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(c.positions, inv, table)
+    scale, err = hd ** -0.5, _err()
+    # two kernels
+    k1, v1 = c.k.clone(), c.v.clone()
+    q = torch.empty(T, nh, hd, dtype=torch.bfloat16, device=DEV)
+    ops.rope_kv_write_partial(parts, bias, q, c.positions, c.tok_seg, table, hd, k1, v1, c.bt, c.num_pages, 1 << 20, nkv, err)
+    want = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    mk = lambda: (torch.full((T, nh, nsplit, hd), float("nan"), device=DEV), torch.full((T, nh, nsplit, 2), float("nan"), device=DEV))
+    po, pml = mk()
+    ops.attention_decode_bf16(q, want, k1, v1, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, nsplit, po, pml,
+                              err, fused_merge=False, cluster=False)
+    ref = ref_paged_attention(q, k1, v1, c.bt, c.positions, c.tok_seg, window, scale)
+    assert int(err) == 0 and torch.allclose(want.float(), ref, atol=2e-2, rtol=2e-2)
+    # one kernel
+    k2, v2 = c.k.clone(), c.v.clone()
+    for t, n in enumerate(ctxs):
+        k2[int(c.bt[t, n // P]), n % P] = float("nan")
+        v2[int(c.bt[t, n // P]), n % P] = float("nan")
+    for _ in range(2):
+        got = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        po, pml = mk()
+        ops.attention_decode_qkv_bf16(parts, bias, table, 1 << 20, got, k2, v2, c.bt, c.positions, c.tok_seg, c.num_pages,
+                                      nh, window, scale, nsplit, po, pml, err, fused_merge=merge == "last_cta")
+        assert int(err) == 0 and not torch.isnan(got.float()).any()
+        assert torch.allclose(got.float(), want.float(), atol=4e-3, rtol=1e-2), float((got.float() - want.float()).abs().max())
+    # the caches agree wherever a request owns the slot (both hold NaN elsewhere)
+    assert torch.equal(torch.isnan(k2), torch.isnan(k1)) and torch.equal(torch.isnan(v2), torch.isnan(v1))
+    assert torch.allclose(k2.float().nan_to_num(), k1.float().nan_to_num(), atol=1e-2, rtol=1e-2)
+    assert torch.allclose(v2.float().nan_to_num(), v1.float().nan_to_num(), atol=1e-2, rtol=1e-2)
+
+
+def test_attention_decode_qkv_reports_a_position_out_of_range():
+    ops = _ops()
+    nh, nkv, hd, P = 4, 2, 64, 16
+    c = PagedCase([(20, 1), (5, 1)], nh, nkv, hd, P, torch.bfloat16, seed=28)
+    parts = _rand((2, c.T, (nh + 2 * nkv) * hd), torch.float32, 62)
+    table = torch.zeros(c.T, hd // 2, 2, dtype=torch.float32, device=DEV)
+    err = _err()
+    ops.attention_decode_qkv_bf16(parts, None, table, 20, torch.empty(c.T, nh * hd, dtype=torch.bfloat16, device=DEV),
+                                  c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, nh, None, hd ** -0.5, 2,
+                                  torch.empty(c.T, nh, 2, hd, device=DEV), torch.empty(c.T, nh, 2, 2, device=DEV), err)
+    torch.cuda.synchronize()
+    assert int(err) != 0                     # position 20 with max_pos 20
+
+
 PREFILL_CASES = [
     (28, 4, 128, 256, None, [(0, 200), (300, 1), (64, 64), (5, 63), (0, 1), (1000, 65)]),
     (8, 8, 64, 16, None, [(0, 130), (17, 2)]),
