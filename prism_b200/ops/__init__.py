@@ -691,21 +691,22 @@ def attention_prefill_bf16(q, out, k_cache, v_cache, block_table, seg_start, cac
 
 
 PREFILL_SPLIT_MIN_TILES = 16      # key tiles (of 64) a split CTA should keep
-PREFILL_SPLIT_FROM_TILES = 64     # fewer key tiles than this are not split: the merge costs as much as it saves
+PREFILL_SPLIT_FROM_TILES = 64     # fewer key tiles than this are not split: the merge costs as much as it saves ...
+PREFILL_SPLIT_FROM_TILES_FEW_CTAS = 32    # ... unless the query tiles fill under a quarter of the GPU
 
 
 def prefill_splits(S: int, max_q_len: int, nh: int, max_kv_len: int, window: Optional[int]) -> int:
     """CTAs that share the key tiles of one (head, 128 query rows) in the tcgen05 prefill kernel: 1 unless
     the query tiles alone leave most of the GPU idle and the keys are many (a short portion against a
     long cache); then as many as fill the two CTAs per SM, each with at least PREFILL_SPLIT_MIN_TILES.
-    (Measured at the 7B head counts, 128 new tokens: 2,048 cached 44 us whole and 65 us in 2 splits;
-    8,192 cached 127 -> 46 us in 8; 32,768 cached 471 -> 86 us in 10.)"""
+    (Measured at the 7B head counts, 128 new tokens: 2,048 cached 42 -> 34 us in 2 splits, 8,192 cached
+    127 -> 46 us in 8, 32,768 cached 471 -> 86 us in 10; 512 new tokens after 2,048: 48 us whole, 55 us in 2.)"""
     if os.environ.get("PRISM_PREFILL_SPLITS"):
         return int(os.environ["PRISM_PREFILL_SPLITS"])
     ctas = S * nh * ((max_q_len + 127) // 128)
     span = min(max_kv_len, window + max_q_len) if window else max_kv_len
     tiles = (span + 63) // 64
-    if tiles < PREFILL_SPLIT_FROM_TILES:
+    if tiles < (PREFILL_SPLIT_FROM_TILES_FEW_CTAS if 4 * ctas <= 2 * NUM_SMS else PREFILL_SPLIT_FROM_TILES):
         return 1
     return max(1, min((2 * NUM_SMS) // max(1, ctas), tiles // PREFILL_SPLIT_MIN_TILES, 16))
 
@@ -760,6 +761,10 @@ def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
     return bool(lib().prism_attention_bf16_supported(hd, nh, nkv))
 
 
+DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what the balance gains (batch 64: 8,192 keys
+                                    # 203 -> 201 us in 4 splits, 32,768 keys 717 -> 673 us)
+
+
 def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> int:
     """How many CTAs share one (token, kv head)'s keys: as many as fill one wave
     of two CTAs per SM, at most one per 64-key tile.  More, shorter CTAs lose:
@@ -770,6 +775,19 @@ def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> i
     tiles = max(1, (span + 63) // 64)
     fill = (2 * NUM_SMS) // max(1, T * nkv)
     n = max(1, min(tiles, 64, fill))
+    if n == 1 and tiles >= DECODE_BALANCE_FROM_TILES:
+        # A large batch against long contexts: one CTA per (token, kv head) fills the GPU, but unevenly (256
+        # CTAs are two on 108 SMs and one on 40, and the kernel lasts as long as the pairs).  A few splits
+        # make the CTAs small enough to spread evenly: the fewest (each keeping 16 tiles or more) that
+        # load every SM to within 5 % of the busiest.
+        def balance(k):
+            m = T * nkv * k / NUM_SMS
+            return m / -(-m // 1)
+        for k in range(1, 9):
+            if k > 1 and tiles // k < 16:
+                break
+            if balance(k) >= 0.95:
+                return k
     if CLUSTER_MERGE and 8 < n <= 12:
         n = 8                                         # one cluster of 8 rather than a few more splits through memory
     return n
