@@ -1,0 +1,28 @@
+"""How many CTAs share the keys of a query tile (prefill) or of a (token, kv head) (decode): the
+host-side choices of ``prism_b200.ops``, which need no GPU."""
+
+from prism_b200 import ops
+
+
+def test_prefill_splits_choice():
+    """Splits only when the query tiles leave the GPU idle and the keys are many."""
+    assert ops.prefill_splits(1, 2048, 28, 2048, None) == 1          # 448 CTAs already
+    assert ops.prefill_splits(1, 128, 28, 640, None) == 1            # 10 key tiles: not worth a merge
+    assert ops.prefill_splits(1, 128, 28, 2048 + 128, None) == 2     # few CTAs: worth it from 2,048 keys
+    assert ops.prefill_splits(1, 512, 28, 2048 + 512, None) == 1
+    n = ops.prefill_splits(1, 128, 28, 32768 + 128, None)
+    assert 2 <= n <= 16 and 28 * n <= 2 * ops.NUM_SMS
+    assert ops.prefill_splits(1, 128, 28, 32768 + 128, 512) == 1     # a window of 512 keys: few tiles
+    assert ops.prefill_splits(4, 256, 28, 32768, None) == 1
+
+
+def test_decode_splits_choice():
+    """As many splits as fill one wave; a batch that fills the GPU unevenly gets a few splits once the
+    contexts are long enough to pay for the merge."""
+    assert ops.decode_splits(8, 4, 2100, None) == 9                  # 288 CTAs for 296 places
+    assert ops.decode_splits(1, 4, 2100, None) == 33                 # one per 64-key tile
+    assert ops.decode_splits(64, 4, 2100, None) == 1                 # short contexts: no merge
+    assert ops.decode_splits(64, 4, 8192, None) == 1
+    assert ops.decode_splits(64, 4, 32768, None) == 4                # 256 CTAs would be 2 + 1 per SM
+    assert ops.decode_splits(74, 4, 32768, None) == 1                # 296 CTAs: even already
+    assert ops.decode_splits(64, 4, 32768, 512) == 1                 # a window of 512 keys is a short context
