@@ -757,6 +757,28 @@ ATTENTION_TC = os.environ.get("PRISM_ATTN_TC", "1") != "0"
 ATTENTION_TC_MIN_Q = int(os.environ.get("PRISM_ATTN_TC_MIN_Q", "64"))     # shorter portions: 64-row mma.sync tiles
 
 
+LONG_CONTEXT = int(os.environ.get("PRISM_LONG_CONTEXT", "4096"))      # keys from which a lone CTA per query tile is too slow
+
+
+def prefill_on_tc(max_q_len: int, max_kv_len: int, window: Optional[int]) -> bool:
+    """Portions of 64 tokens and more go to the tcgen05 kernel (128-row query tiles), shorter ones to the
+    mma.sync kernel (64-row tiles, cheaper to start) - unless the cache is long: the tcgen05 kernel can share
+    a query tile's keys among CTAs, the mma.sync kernel walks them with one CTA per head (128 tokens behind
+    32,768: 86 us against 729 us), and a prompt's last portion can be a few tokens behind all the others."""
+    span = min(max_kv_len, window + max_q_len) if window else max_kv_len
+    return max_q_len >= ATTENTION_TC_MIN_Q or span >= LONG_CONTEXT
+
+
+def decoders_apart(n_leading_single: int, their_max_kv_len: int, window: Optional[int]) -> bool:
+    """In a mixed step: whether the decoding requests at the head of the batch go to the decode kernel.  Worth
+    a launch of its own from ``MIXED_SPLIT_MIN`` of them on - or from one, if their contexts are long: as
+    one-token segments of the prefill kernel each would be a single CTA per head walking all its keys."""
+    if n_leading_single <= 0:
+        return False
+    span = min(their_max_kv_len, window + 64) if window else their_max_kv_len
+    return n_leading_single >= MIXED_SPLIT_MIN or span >= LONG_CONTEXT
+
+
 def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
     return bool(lib().prism_attention_bf16_supported(hd, nh, nkv))
 
@@ -820,7 +842,7 @@ def _attention_portions(ctx, q, out, cache, window, scale, first_seg: int):
     T, nh, hd = q.shape
     nkv = cache.k.shape[2]
     seg_start, cached_len, bt = ctx.seg_start[first_seg:], ctx.cached_len[first_seg:], cache.block_table[first_seg:]
-    if (ATTENTION_TC and ctx.max_q_len >= ATTENTION_TC_MIN_Q and scale > 0 and cache.k.is_contiguous()
+    if (ATTENTION_TC and prefill_on_tc(ctx.max_q_len, ctx.max_kv_len, window) and scale > 0 and cache.k.is_contiguous()
             and cache.v.is_contiguous() and attention_prefill_tc_supported(hd, nh, nkv, cache.k.shape[1])):
         ns = prefill_splits(cached_len.shape[0], ctx.max_q_len, nh, ctx.max_kv_len, window)
         attention_prefill_tc(q, out, cache.k, cache.v, bt, seg_start, cached_len, ctx.max_q_len, cache.num_pages,
@@ -841,8 +863,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
     nkv = cache.k.shape[2]
     if q.dtype == torch.bfloat16 and not FORCE_GENERIC_ATTENTION and attention_bf16_supported(hd, nh, nkv):
         nd = T if ctx.decode_only else _leading_single_token_segments(ctx)
-        if nd < MIXED_SPLIT_MIN and not ctx.decode_only:
-            nd = 0
+        if not ctx.decode_only:
+            longest = max(ctx.host["cached_len"][:nd]) + 1 if nd else 0      # keys of the longest decoding request
+            if not decoders_apart(nd, longest, window):
+                nd = 0
         if nd > 0:
             nsplit = decode_splits(nd, nkv, ctx.max_kv_len, window)
             part_o = ctx.alloc((nd, nh, nsplit, hd), torch.float32)

@@ -196,7 +196,13 @@ def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypat
     cfg = dict(SHAPE_7B, vocab_size=152064)
     prompt = random_tokens(150000, 6000, 4)
     logits = {}
-    for mode in ("fast", "generic", "portions", "short_portions"):
+    calls = {"decode_tokens": [], "prefill_splits": []}
+    real_decode, real_tc = ops.attention_decode_bf16, ops.attention_prefill_tc
+    monkeypatch.setattr(ops, "attention_decode_bf16",
+                        lambda q, *a, **k: (calls["decode_tokens"].append(q.shape[0]), real_decode(q, *a, **k))[1])
+    monkeypatch.setattr(ops, "attention_prefill_tc",
+                        lambda *a, **k: (calls["prefill_splits"].append(k.get("nsplit", 1)), real_tc(*a, **k))[1])
+    for mode in ("fast", "generic", "portions", "short_portions", "tail_and_mixed"):
         monkeypatch.setattr(ops, "FORCE_GENERIC_ATTENTION", mode == "generic")
         eng = Engine(None, EngineConfig(kv_page_size=256, num_pages=32, max_seq_len=8192, use_cuda_graph=mode != "generic"),
                      dtype="bfloat16", config=cfg, random_seed=0)
@@ -211,6 +217,24 @@ def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypat
             r.step([Segment(0, prompt[:4936], [])])
             for c in range(4936, 6000, 152):
                 lg = r.step([Segment(0, prompt[c:c + 152], [151])])
+        elif mode == "tail_and_mixed":
+            # the prompt's last 32 tokens as a portion of their own: short, but behind 5,968 keys, so the
+            # tcgen05 kernel with shared keys takes it; then the first decoded token beside another request's
+            # prompt portion: one decoding request only, but a long one, so it goes to the decode kernel
+            r.step([Segment(0, prompt[:5968], [])])
+            calls["prefill_splits"].clear()
+            lg = r.step([Segment(0, prompt[5968:], [31])])
+            assert calls["prefill_splits"] and min(calls["prefill_splits"]) > 1, calls
+            r.begin_request(1)
+            calls["decode_tokens"].clear()
+            first = r.step([Segment(0, [100], [0]), Segment(1, prompt[:100], [])])
+            assert calls["decode_tokens"] and set(calls["decode_tokens"]) == {1}, calls
+            outs = [lg.float().cpu(), first.float().cpu()]
+            outs += [r.step([Segment(0, [100 + s], [0])]).float().cpu() for s in range(1, 4)]
+            r.check_errors()
+            logits[mode] = outs
+            del eng, r
+            continue
         else:
             lg = r.step([Segment(0, prompt, [5999])])
         outs = [lg.float().cpu()] + [r.step([Segment(0, [100 + s], [0])]).float().cpu() for s in range(4)]
@@ -218,6 +242,6 @@ def test_long_prompt_on_the_fast_kernels_against_the_generic_attention(monkeypat
         logits[mode] = outs
         del eng, r
     scale = float(logits["fast"][0].abs().max())
-    for mode in ("generic", "portions", "short_portions"):
+    for mode in ("generic", "portions", "short_portions", "tail_and_mixed"):
         for a, b in zip(logits["fast"], logits[mode]):
             assert float((a - b).abs().max()) <= 0.03 * scale, (mode, float((a - b).abs().max()), scale)

@@ -26,3 +26,19 @@ def test_decode_splits_choice():
     assert ops.decode_splits(64, 4, 32768, None) == 4                # 256 CTAs would be 2 + 1 per SM
     assert ops.decode_splits(74, 4, 32768, None) == 1                # 296 CTAs: even already
     assert ops.decode_splits(64, 4, 32768, 512) == 1                 # a window of 512 keys is a short context
+
+
+def test_prefill_kernel_choice():
+    """64 tokens and more: the tcgen05 kernel; fewer: the mma.sync kernel, unless the cache is long."""
+    assert ops.prefill_on_tc(64, 64, None) and ops.prefill_on_tc(2048, 2048, None)
+    assert not ops.prefill_on_tc(63, 1000, None)
+    assert ops.prefill_on_tc(5, 6000, None)                          # a prompt's last few tokens behind the rest
+    assert not ops.prefill_on_tc(5, 6000, 512)                       # a window keeps the keys few
+
+
+def test_decoders_leave_a_mixed_step_for_the_decode_kernel():
+    assert not ops.decoders_apart(0, 0, None)
+    assert not ops.decoders_apart(3, 2000, None)                     # a few short ones stay with the portions
+    assert ops.decoders_apart(ops.MIXED_SPLIT_MIN, 100, None)
+    assert ops.decoders_apart(1, 6001, None)                         # one long context is enough
+    assert not ops.decoders_apart(1, 6001, 512)
