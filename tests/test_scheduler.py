@@ -175,8 +175,14 @@ def test_sampling_counter_is_the_number_of_generated_tokens():
 # --------------------------------------------------------------------------
 
 class PipelinedRunner(FakeRunner):
-    def can_run(self, segments):
-        return all(self.cache.can_append(s.req_id, len(s.tokens)) for s in segments)
+    def can_run(self, segments):                           # as ModelRunner.can_run: all of them together
+        reserve = [0] * len(self.cache.groups)
+        for s in segments:
+            if not self.cache.can_append(s.req_id, len(s.tokens), reserve):
+                return False
+            for g, n in enumerate(self.cache.pages_needed(s.req_id, len(s.tokens))):
+                reserve[g] += n
+        return True
 
     def step(self, segments, token_source=None):
         if token_source is not None:                       # "device" tokens of the step in flight
@@ -243,3 +249,79 @@ def test_pipelined_decoding_stops_at_eos_and_drops_the_token_in_flight():
     assert a.generated_tokens == want_a[:want_a.index(eos) + 1] and a.finish_reason == "stop"
     assert b.generated_tokens == expected([9, 9], 8) and b.finish_reason == "length"
     assert runner.cache.pages_in_use() == 0
+
+
+# --------------------------------------------------------------------------
+# random workloads
+# --------------------------------------------------------------------------
+
+class WindowedRunner(FakeRunner):
+    """Two cache groups: all keys, and a window of 6 (whose pages come back as the window passes)."""
+
+    def __init__(self, num_pages, page_size=4, max_seqs=8, max_seq_len=256):
+        groups, _ = plan_groups([CacheNeed("paged", 1, 8, None), CacheNeed("paged", 1, 8, 6)], [None, None])
+        self.cache = CacheManager(groups, page_size, num_pages, max_seqs, max_seq_len)
+        self.history, self.steps = {}, []
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_random_workloads_finish_with_the_same_tokens_and_no_page_lost(seed):
+    """Random prompts, lengths, arrival times, budgets and pool sizes (many of them too small for
+    everybody at once): every request ends with the tokens it would get alone, whatever was cut,
+    made to wait, preempted and recomputed; the pool is whole again at the end."""
+    import random
+    rnd = random.Random(seed)
+    page_size = rnd.choice([2, 4, 8])
+    n_req = rnd.randint(3, 12)
+    specs = [([rnd.randrange(V) for _ in range(rnd.randint(1, 40))], rnd.randint(1, 20)) for _ in range(n_req)]
+    biggest = max((len(p) + n + page_size - 1) // page_size for p, n in specs)
+    num_pages = biggest + rnd.randint(0, 2 * biggest)                  # from "one request at a time" to roomy
+    runner = (WindowedRunner if seed % 3 == 0 else FakeRunner)(num_pages, page_size, max_seqs=rnd.randint(1, 6))
+    cfg = SchedulerConfig(max_batch_tokens=rnd.choice([4, 16, 64]), max_num_seqs=rnd.randint(1, 8),
+                          prefill_chunk=rnd.choice([3, 8, 64]), async_decode=False)
+    s = Scheduler(runner, FakeSampler(), cfg)
+    arrivals = sorted(rnd.randint(0, 30) for _ in specs)
+    reqs, steps = [], 0
+    while len(reqs) < n_req or s.has_work():
+        while len(reqs) < n_req and arrivals[len(reqs)] <= steps:
+            p, n = specs[len(reqs)]
+            reqs.append(s.add_request(p, SamplingParams(max_new_tokens=n)))
+        if s.has_work():
+            planned_before = s.stats.steps
+            s.step()
+            assert s.stats.steps == planned_before + 1, "a step with work to do ran nothing"
+            assert sum(n for _, n, _ in runner.steps[-1]) <= cfg.max_batch_tokens
+        steps += 1
+        assert steps < 5000, "the scheduler does not come to an end"
+    for (p, n), r in zip(specs, reqs):
+        assert r.state == RequestState.FINISHED and r.generated_tokens == expected(p, n), (r.id, r.num_preemptions)
+    assert runner.cache.pages_in_use() == 0 and not runner.cache.requests
+    runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_random_workloads_with_pipelined_decoding_and_eos(seed):
+    """The same with an end-of-sequence token and pipelined decoding (one step always in flight while
+    only decoding requests run): tokens as alone, cut at the first eos; nothing lost."""
+    import random
+    rnd = random.Random(1000 + seed)
+    page_size = rnd.choice([2, 4, 8])
+    eos = rnd.randrange(V)
+    specs = [([rnd.randrange(V) for _ in range(rnd.randint(1, 30))], rnd.randint(1, 25), rnd.random() < 0.3)
+             for _ in range(rnd.randint(2, 10))]
+    biggest = max((len(p) + n + page_size - 1) // page_size for p, n, _ in specs)
+    runner = PipelinedRunner(biggest + rnd.randint(0, 2 * biggest), page_size, max_seqs=rnd.randint(1, 6))
+    cfg = SchedulerConfig(max_batch_tokens=rnd.choice([8, 64]), max_num_seqs=rnd.randint(1, 8),
+                          prefill_chunk=rnd.choice([5, 64]), async_decode=True)
+    sampler = PipelinedSampler()
+    s = Scheduler(runner, sampler, cfg, eos_token_id=eos)
+    reqs = [s.add_request(p, SamplingParams(max_new_tokens=n, ignore_eos=ig)) for p, n, ig in specs]
+    s.run_to_completion()
+    for (p, n, ig), r in zip(specs, reqs):
+        want = expected(p, n)
+        if not ig and eos in want:
+            want = want[:want.index(eos) + 1]
+        assert r.generated_tokens == want, (r.id, r.num_preemptions, r.finish_reason)
+        assert r.finish_reason == ("stop" if (not ig and want[-1] == eos) else "length")
+    assert runner.cache.pages_in_use() == 0 and not runner.cache.requests
+    runner.cache.check_invariants()
