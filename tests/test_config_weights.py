@@ -156,3 +156,56 @@ def test_random_weights_are_a_function_of_config_and_seed(tmp_path):
     assert abs(float(n.mean()) - 1.0) < 2e-2
     with open(tmp_path / "x" / "config.json") as f:
         assert json.load(f)["architectures"] == ["Qwen2ForCausalLM"]
+
+
+def _split_into_shards(folder, with_index):
+    """Rewrite model.safetensors as two shards: the q/k/v of every layer land in different files."""
+    path = os.path.join(folder, "model.safetensors")
+    t = load_file(path)
+    names = sorted(t)
+    a = {n: t[n] for i, n in enumerate(names) if i % 2 == 0}
+    b = {n: t[n] for i, n in enumerate(names) if i % 2 == 1}
+    os.remove(path)
+    save_file(a, os.path.join(folder, "model-00001-of-00002.safetensors"))
+    save_file(b, os.path.join(folder, "model-00002-of-00002.safetensors"))
+    if with_index:
+        wm = {n: "model-00001-of-00002.safetensors" for n in a}
+        wm.update({n: "model-00002-of-00002.safetensors" for n in b})
+        with open(os.path.join(folder, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {}, "weight_map": wm}, f)
+    return t
+
+
+@pytest.mark.parametrize("with_index", [True, False])
+def test_sharded_folder_loads_like_a_single_file(tmp_path, with_index):
+    d = write_model_folder(TINY_B, 5, str(tmp_path / "m"))
+    _, _, whole = load_model_folder(d, "cpu", torch.bfloat16)
+    whole = {k: v.clone() for k, v in whole.tensors.items() if v is not None}
+    _split_into_shards(d, with_index)
+    _, _, pool = load_model_folder(d, "cpu", torch.bfloat16)
+    assert set(whole) == {k for k, v in pool.tensors.items() if v is not None}
+    assert all(torch.equal(pool[k], v) for k, v in whole.items())
+
+
+def test_tensor_in_two_shards_is_an_error(tmp_path):
+    d = write_model_folder(TINY_B, 5, str(tmp_path / "m"))
+    t = _split_into_shards(d, with_index=False)
+    extra = load_file(os.path.join(d, "model-00002-of-00002.safetensors"))
+    extra["model.norm.weight"] = t["model.norm.weight"]
+    extra["model.embed_tokens.weight"] = t["model.embed_tokens.weight"]
+    save_file(extra, os.path.join(d, "model-00002-of-00002.safetensors"))
+    with pytest.raises(WeightError) as e:
+        load_model_folder(d, "cpu", torch.bfloat16)
+    assert "more than one shard" in str(e.value) and "model.norm.weight" in str(e.value)
+
+
+def test_half_precision_files_are_kept_in_bf16_and_float32_engine_upcasts(tmp_path):
+    d = write_model_folder(TINY_A, 2, str(tmp_path / "m"))
+    path = os.path.join(d, "model.safetensors")
+    t = {k: v.to(torch.float16) for k, v in load_file(path).items()}
+    save_file(t, path)
+    _, _, pool = load_model_folder(d, "cpu", torch.bfloat16)
+    assert all(v.dtype == torch.bfloat16 for v in pool.tensors.values() if v is not None)
+    assert torch.equal(pool["final_norm.weight"], t["model.norm.weight"].to(torch.bfloat16))
+    _, _, pool32 = load_model_folder(d, "cpu", torch.float32)
+    assert torch.equal(pool32["final_norm.weight"], t["model.norm.weight"].float())
