@@ -787,17 +787,20 @@ DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what t
                                     # 203 -> 201 us in 4 splits, 32,768 keys 717 -> 673 us)
 
 
-def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int]) -> int:
+def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int], balance: bool = True) -> int:
     """How many CTAs share one (token, kv head)'s keys: as many as fill one wave
     of two CTAs per SM, at most one per 64-key tile.  More, shorter CTAs lose:
-    each pays the same fixed latencies (position, block table, first bytes, merge)."""
+    each pays the same fixed latencies (position, block table, first bytes, merge).  ``max_kv_len`` is the
+    longest context of the batch, or, when a graph is captured, the longest the graph may ever see;
+    ``balance`` (the few splits of a large batch against long contexts) is for the former only: a bound
+    of 32,768 says nothing about the contexts a replay will meet."""
     if os.environ.get("PRISM_DECODE_SPLITS"):
         return int(os.environ["PRISM_DECODE_SPLITS"])
     span = min(max_kv_len, window + 64) if window else max_kv_len
     tiles = max(1, (span + 63) // 64)
     fill = (2 * NUM_SMS) // max(1, T * nkv)
     n = max(1, min(tiles, 64, fill))
-    if n == 1 and tiles >= DECODE_BALANCE_FROM_TILES:
+    if balance and n == 1 and tiles >= DECODE_BALANCE_FROM_TILES:
         # A large batch against long contexts: one CTA per (token, kv head) fills the GPU, but unevenly (256
         # CTAs are two on 108 SMs and one on 40, and the kernel lasts as long as the pairs).  A few splits
         # make the CTAs small enough to spread evenly: the fewest (each keeping 16 tiles or more) that
@@ -868,7 +871,7 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
             if not decoders_apart(nd, longest, window):
                 nd = 0
         if nd > 0:
-            nsplit = decode_splits(nd, nkv, ctx.max_kv_len, window)
+            nsplit = decode_splits(nd, nkv, ctx.max_kv_len, window, balance=ctx.host is not None)
             part_o = ctx.alloc((nd, nh, nsplit, hd), torch.float32)
             part_ml = ctx.alloc((nd, nh, nsplit, 2), torch.float32)
             attention_decode_bf16(q[:nd], out[:nd], cache.k, cache.v, cache.block_table, ctx.positions[:nd],
@@ -909,7 +912,7 @@ def qkv_attention(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[tor
                 rope_table(ctx.positions, rot.inv_freq, table)
             parts = ctx.alloc((ks, T, (nh + 2 * nkv) * hd), torch.float32)
             gemm_tc(x, qkv_w, None, parts, EPI_PARTIAL, ksplit=ks)
-            nsplit = decode_splits(T, nkv, ctx.max_kv_len, window)
+            nsplit = decode_splits(T, nkv, ctx.max_kv_len, window, balance=ctx.host is not None)
             part_o = ctx.alloc((T, nh, nsplit, hd), torch.float32)
             part_ml = ctx.alloc((T, nh, nsplit, 2), torch.float32)
             attention_decode_qkv_bf16(parts, qkv_b, table, ctx.max_positions, out, cache.k, cache.v, cache.block_table,

@@ -26,6 +26,8 @@ def test_decode_splits_choice():
     assert ops.decode_splits(64, 4, 32768, None) == 4                # 256 CTAs would be 2 + 1 per SM
     assert ops.decode_splits(74, 4, 32768, None) == 1                # 296 CTAs: even already
     assert ops.decode_splits(64, 4, 32768, 512) == 1                 # a window of 512 keys is a short context
+    assert ops.decode_splits(64, 4, 32768, None, balance=False) == 1     # a captured graph knows a bound only
+    assert ops.decode_splits(8, 4, 32768, None, balance=False) == 9
 
 
 def test_prefill_kernel_choice():
