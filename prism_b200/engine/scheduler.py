@@ -20,6 +20,14 @@ When pages run out:
     recomputed from prompt + generated tokens (its sampling counter is the
     number of generated tokens, so its draws do not change);
   * a request that could not fit even alone is refused at ``add_request``.
+A plan that had to preempt admits nobody in the same call, and a request that
+has been preempted before is admitted again, while others run, only when the
+free pages hold all it has to recompute plus a page of growth for everyone
+running: the few pages that a preemption leaves would otherwise go back to the
+victim, which would recompute a portion only to be thrown out again a step later.
+
+A sequence ends at any of the model's end-of-sequence ids (config.json may
+list several) or at the request's own ``SamplingParams.eos_token_id``.
 """
 
 from __future__ import annotations
@@ -27,7 +35,7 @@ from __future__ import annotations
 import time
 from collections import deque
 from dataclasses import dataclass
-from typing import Deque, List, Optional, Tuple
+from typing import Deque, FrozenSet, List, Optional, Tuple
 
 from ..config.engine_config import SchedulerConfig
 from ..sampling.rng import uniform
@@ -47,17 +55,26 @@ class SchedulerStats:
     preemptions: int = 0
 
 
+def eos_set(eos) -> FrozenSet[int]:
+    """None, one id or several ids as a set."""
+    if eos is None:
+        return frozenset()
+    if isinstance(eos, int):
+        return frozenset((eos,))
+    return frozenset(int(e) for e in eos)
+
+
 class Scheduler:
     """``runner`` needs ``cache`` (a CacheManager), ``begin_request``,
     ``end_request`` and ``step(segments) -> logits``; ``sampler`` needs
     ``sample(logits, temperatures, us) -> token ids``."""
 
     def __init__(self, runner, sampler, config: Optional[SchedulerConfig] = None,
-                 eos_token_id: Optional[int] = None, seed: int = 0):
+                 eos_token_id=None, seed: int = 0):
         self.runner, self.sampler = runner, sampler
         self.cache = runner.cache
         self.config = config or SchedulerConfig()
-        self.eos_token_id = eos_token_id
+        self.eos_token_ids = eos_set(eos_token_id)       # one id, several, or none
         self.seed = seed
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []          # in admission order
@@ -107,6 +124,14 @@ class Scheduler:
         for g, k in enumerate(self.cache.pages_needed(req_id, n)):
             reserve[g] += k
 
+    def _room_to_recompute(self, req: Request, reserve: List[int]) -> bool:
+        """Whether the free pages hold every token ``req`` has so far, one more, and a page of growth
+        for each running request (groups with a window need a few pages only and are not asked)."""
+        P = self.cache.page_size
+        want = (len(req.prompt_tokens) + len(req.generated_tokens) + 1 + P - 1) // P + len(self.running)
+        return all(self.cache.allocators[g.index].num_free - reserve[g.index] >= want
+                   for g in self.cache.groups if g.kind == "paged" and g.need.window is None)
+
     def _preempt(self, req: Request) -> None:
         self.runner.end_request(req.id)
         self.running.remove(req)
@@ -121,6 +146,7 @@ class Scheduler:
         Admits and preempts as a side effect; launches nothing."""
         cfg = self.config
         has_paged = any(g.kind == "paged" for g in self.cache.groups)
+        preempted = False
         while True:
             reserve = [0] * len(self.cache.groups)
             batch: List[Tuple[Request, int]] = []
@@ -138,6 +164,7 @@ class Scheduler:
                 budget -= 1
             if victim is not None:
                 self._preempt(victim)
+                preempted = True
                 continue
             # 2. portions of prompts already admitted
             for req in self.running:
@@ -151,8 +178,10 @@ class Scheduler:
                     budget -= n
             # 3. admissions
             while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs \
-                    and self.cache.has_free_slot():
+                    and self.cache.has_free_slot() and not (preempted and self.running):
                 req = self.waiting[0]
+                if req.num_preemptions and self.running and has_paged and not self._room_to_recompute(req, reserve):
+                    break
                 self.runner.begin_request(req.id)
                 n = min(req.remaining, cfg.prefill_chunk, budget)
                 n = self._fits(req.id, n, reserve) if has_paged else n
@@ -169,6 +198,7 @@ class Scheduler:
                 return batch
             # nothing can move although requests are running: free the newest one's pages
             self._preempt(self.running[-1])
+            preempted = True
 
     # ---- one step -----------------------------------------------------------------
     def step(self) -> List[Tuple[Request, int]]:
@@ -208,10 +238,16 @@ class Scheduler:
                 self._maybe_finish(req, int(tok), now)
         return out
 
+    def _ends(self, req: Request, tok: int) -> bool:
+        """Whether ``tok`` is an end-of-sequence token for this request."""
+        if req.params.ignore_eos:
+            return False
+        eos = eos_set(req.params.eos_token_id) if req.params.eos_token_id is not None else self.eos_token_ids
+        return tok in eos
+
     def _maybe_finish(self, req: Request, tok: int, now: float) -> None:
-        eos = req.params.eos_token_id if req.params.eos_token_id is not None else self.eos_token_id
         reason = None
-        if eos is not None and tok == eos and not req.params.ignore_eos:
+        if self._ends(req, tok):
             reason = "stop"                      # the eos token stays in the output (scheduler.py:245)
         elif len(req.generated_tokens) >= req.params.max_new_tokens:
             reason = "length"
@@ -278,8 +314,7 @@ class Scheduler:
                 req.num_computed += 1
                 req.generated_tokens.append(int(tok))
                 self.stats.tokens_generated += 1
-                eos = req.params.eos_token_id if req.params.eos_token_id is not None else self.eos_token_id
-                if eos is not None and int(tok) == eos and not req.params.ignore_eos:
+                if self._ends(req, int(tok)):
                     req.finish_reason = "stop"
                 elif len(req.generated_tokens) >= req.params.max_new_tokens:
                     req.finish_reason = "length"

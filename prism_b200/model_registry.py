@@ -7,6 +7,12 @@ andre-fu/prism's file of this name is a checkpoint LRU
 substring allow-list (engine/server.py:171-173) and a shape tuple
 (engine/scheduler.py:25-28).  This registry is the missing map from a name to
 code.
+
+An architecture is a module under ``prism_b200/models`` that calls
+``register_architecture`` when it is imported; every module of that package
+is imported the first time a name is looked up, so adding an architecture
+adds a file and edits none.  (Code outside the package may register one at
+any time by calling ``register_architecture`` itself.)
 """
 
 from __future__ import annotations
@@ -14,9 +20,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Callable, Dict
 
-from .config.model_config import ConfigError, Qwen2Config
+import importlib
+import pkgutil
+
+from .config.model_config import ConfigError
 from .models.decoder import DecoderModel, ModelSpec
-from .models.qwen2 import qwen2_spec
 
 
 @dataclass
@@ -33,12 +41,28 @@ def register_architecture(name: str, parse_config, build_spec) -> None:
     _ARCHITECTURES[name] = Architecture(name, parse_config, build_spec)
 
 
+_builtin_loaded = False
+
+
+def _load_builtin() -> None:
+    """Import every module of ``prism_b200.models`` once (each registers its architecture)."""
+    global _builtin_loaded
+    if _builtin_loaded:
+        return
+    _builtin_loaded = True
+    from . import models
+    for m in pkgutil.iter_modules(models.__path__):
+        importlib.import_module(f"{models.__name__}.{m.name}")
+
+
 def registered_architectures():
+    _load_builtin()
     return sorted(_ARCHITECTURES)
 
 
 def resolve(raw_config: dict) -> Architecture:
     """The architecture a raw config.json names."""
+    _load_builtin()
     archs = raw_config.get("architectures") or []
     if not archs:
         raise ConfigError(f"config.json has no 'architectures'; registered: {registered_architectures()}")
@@ -53,6 +77,3 @@ def build_model(raw_config: dict):
     arch = resolve(raw_config)
     cfg = arch.parse_config(raw_config)
     return cfg, DecoderModel(arch.build_spec(cfg))
-
-
-register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_spec)

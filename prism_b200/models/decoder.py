@@ -34,7 +34,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     schedule: Optional[List[ScheduleEntry]] = None   # default: every layer once, in order
-    eos_token_id: Optional[int] = None
+    eos_token_id: tuple = ()               # every id that ends a sequence
 
     def run_order(self) -> List[ScheduleEntry]:
         return self.schedule if self.schedule is not None else [ScheduleEntry(i) for i in range(len(self.layers))]

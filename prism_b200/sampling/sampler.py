@@ -26,7 +26,7 @@ class SamplingParams:
     max_new_tokens: int = 100
     temperature: float = 0.0
     seed: Optional[int] = None
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[object] = None     # one id or several; None: the model's own
     ignore_eos: bool = False
 
 

@@ -45,8 +45,7 @@ def write_model_folder(raw_config: dict, seed: int, out_dir: str,
                        store_dtype: torch.dtype = torch.bfloat16) -> str:
     """Write ``config.json`` and ``model.safetensors`` for ``raw_config``."""
     from safetensors.torch import save_file
-    raw = dict(raw_config)
-    raw.setdefault("architectures", ["Qwen2ForCausalLM"])
+    raw = dict(raw_config)           # must name its architecture, as a config.json does
     _, model = build_model(raw)
     gen = torch.Generator().manual_seed(int(seed))
     tensors = {name: _draw(shape, init, gen).to(store_dtype).contiguous()

@@ -9,7 +9,8 @@ from safetensors.torch import load_file, save_file
 
 from helpers import TINY_A, TINY_B, TINY_C, model_folder
 
-from prism_b200.config.model_config import ConfigError, Qwen2Config
+from prism_b200.config.model_config import ConfigError
+from prism_b200.models.qwen2 import Qwen2Config
 from prism_b200.model_registry import build_model, registered_architectures, resolve
 from prism_b200.weights.loader import WeightError, load_model_folder
 from prism_b200.weights.random_init import file_tensors, write_model_folder
@@ -25,6 +26,13 @@ def test_config_reads_every_key_and_defaults():
                                    num_attention_heads=4, architectures=["Qwen2ForCausalLM"]))
     assert d.num_key_value_heads == 4 and d.head_dim == 8 and d.rms_norm_eps == 1e-6 and d.rope_theta == 10000.0
     assert d.max_position_embeddings == 4096 and d.tie_word_embeddings is False and d.layer_window(0) is None
+    # end-of-sequence ids: none, one, or a list (all kept)
+    assert d.eos_token_id == ()
+    assert Qwen2Config.from_dict(dict(TINY_A, eos_token_id=7)).eos_token_id == (7,)
+    several = Qwen2Config.from_dict(dict(TINY_A, eos_token_id=[151645, 151643]))
+    assert several.eos_token_id == (151645, 151643) and several.to_dict()["eos_token_id"] == [151645, 151643]
+    _, m = build_model(dict(TINY_A, eos_token_id=[5, 9]))
+    assert m.spec.eos_token_id == (5, 9)
 
 
 @pytest.mark.parametrize("patch,word", [
@@ -45,6 +53,20 @@ def test_config_errors(patch, word):
             raw[k] = v
     with pytest.raises(ConfigError, match=word):
         Qwen2Config.from_dict(raw)
+
+
+def test_an_architecture_is_a_module_that_registers_itself():
+    """Nothing outside ``prism_b200/models/qwen2.py`` names the architecture: the registry, the loader, the
+    random-weights mode and the generic configuration module hold no architecture name."""
+    import prism_b200
+    root = os.path.dirname(prism_b200.__file__)
+    for rel in ("model_registry.py", "config/model_config.py", "config/engine_config.py", "weights/random_init.py",
+                "weights/loader.py", "weights/pool.py", "models/decoder.py", "engine/runner.py", "engine/llm.py"):
+        with open(os.path.join(root, rel)) as f:
+            text = f.read()
+        assert "Qwen2" not in text and "qwen2" not in text, rel
+    with pytest.raises(ConfigError, match="architectures"):
+        write_model_folder({k: v for k, v in TINY_A.items() if k != "architectures"}, 0, "/nonexistent")
 
 
 def test_registry():

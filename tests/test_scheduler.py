@@ -116,6 +116,35 @@ def test_eos_stops_and_is_kept_and_ignore_eos():
     assert q.generated_tokens == expected(p, 4) and q.finish_reason == "length"
 
 
+def test_any_of_several_eos_ids_stops():
+    """config.json may list several end-of-sequence ids (chat variants do); each of them ends a request,
+    and a request's own ``eos_token_id`` (one id or a list) replaces the model's."""
+    p = [2, 3, 4]                                       # six different tokens follow
+    toks = expected(p, 6)
+    s, _ = make(eos=[V + 7, toks[2]])                   # the second of the two ids comes up third
+    r = s.add_request(p, SamplingParams(max_new_tokens=6))
+    own = s.add_request(p, SamplingParams(max_new_tokens=6, eos_token_id=[toks[4], V + 9]))
+    one = s.add_request(p, SamplingParams(max_new_tokens=6, eos_token_id=toks[0]))
+    s.run_to_completion()
+    assert r.generated_tokens == toks[:3] and r.finish_reason == "stop"
+    assert own.generated_tokens == toks[:5] and own.finish_reason == "stop"
+    assert one.generated_tokens == toks[:1] and one.finish_reason == "stop"
+
+
+def test_tight_pool_does_not_recompute_over_and_over():
+    """Two requests that do not fit together: the newer one is preempted once and waits until the older
+    one has finished, instead of being admitted again into the few pages left and thrown out a step
+    later.  Bound on the work thrown away: each prompt token is prefilled at most twice."""
+    s, runner = make(num_pages=12, page_size=4, max_batch_tokens=64, prefill_chunk=64, max_num_seqs=4)
+    a = s.add_request([1] * 11, SamplingParams(max_new_tokens=32))
+    b = s.add_request([2] * 11, SamplingParams(max_new_tokens=32))
+    s.run_to_completion()
+    assert a.generated_tokens == expected(a.prompt_tokens, 32) and b.generated_tokens == expected(b.prompt_tokens, 32)
+    assert s.stats.preemptions <= 2
+    assert s.stats.prefill_tokens <= 2 * 22 + 32          # prompts twice at most, plus one recompute of what b had generated
+    assert runner.cache.pages_in_use() == 0
+
+
 def test_refused_at_submission():
     s, _ = make(num_pages=4, page_size=4, max_seq_len=64)
     with pytest.raises(ValueError, match="empty"):
