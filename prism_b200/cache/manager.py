@@ -69,6 +69,29 @@ def plan_groups(cache_needs: Sequence[Optional[CacheNeed]], reads: Sequence[Opti
     return groups, where
 
 
+def pool_sizes(groups: Sequence[CacheGroup], page_size: int, elem_bytes: int, max_seq_len: int, max_seqs: int,
+               max_portion: int, num_pages: Optional[int] = None, budget_bytes: Optional[float] = None) -> List[int]:
+    """Pages of every cache group's pool (0 for groups that are not paged).  Groups that keep all keys
+    get ``num_pages``, or what ``budget_bytes`` pays for once the windowed groups are paid, at most what
+    ``max_seqs`` requests of ``max_seq_len`` tokens hold and at least 16.  A group whose layers see a window
+    needs, per request, the pages under the window and under one step's portion (``max_portion`` tokens)
+    plus one - pages behind the window come back when the step is committed - so it gets that many for
+    every request slot, never more than the other groups."""
+    P = int(page_size)
+    cap = max_seqs * ((max_seq_len + P - 1) // P)
+    page_bytes = {g.index: 2 * g.num_planes * P * g.need.num_kv_heads * g.need.head_dim * elem_bytes
+                  for g in groups if g.kind == "paged"}
+    windowed = {g.index: min(cap, max_seqs * ((g.need.window + max_portion + P - 1) // P + 1))
+                for g in groups if g.kind == "paged" and g.need.window is not None}
+    if num_pages:
+        full = int(num_pages)
+    else:
+        left = float(budget_bytes or 0) - sum(page_bytes[gi] * n for gi, n in windowed.items())
+        per_page = sum(b for gi, b in page_bytes.items() if gi not in windowed) or 1
+        full = max(16, min(int(max(left, 0) // per_page), cap))
+    return [0 if g.kind != "paged" else min(full, windowed.get(g.index, full)) for g in groups]
+
+
 class PageAllocator:
     """LIFO free list over ``num_pages`` pages; page 0 is handed out first and a
     freed page is the next one re-used (kv_cache.py:49,82,90)."""

@@ -17,13 +17,14 @@ from typing import List, Optional, Sequence, Union
 import torch
 
 from ..config.engine_config import EngineConfig, ModelConfig
+from ..cache.manager import pool_sizes
 from ..config.model_config import read_config_json
 from ..model_registry import build_model
 from ..sampling.sampler import Sampler, SamplingParams
 from ..weights.loader import load_weights
 from ..weights.random_init import random_pool
 from .request import GenerationResult
-from .runner import ModelRunner
+from .runner import ModelRunner, cache_groups
 from .scheduler import Scheduler
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -57,23 +58,22 @@ class Engine:
             self.pool = random_pool(self.model, random_seed or 0, self.device, self.dtype)
         spec = self.model.spec
         max_seq_len = min(ec.max_seq_len or spec.max_positions, spec.max_positions)
-        num_pages = ec.num_pages or self._pages_from_budget(ec, max_seq_len)
+        num_pages = self._pages_per_group(ec, max_seq_len)
         self.runner = ModelRunner(self.model, self.device, self.dtype, ec.kv_page_size, num_pages,
                                   ec.scheduler.max_num_seqs, max_seq_len, ec.use_cuda_graph,
                                   ec.graph_batch_sizes)
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(self.runner, self.sampler, ec.scheduler, spec.eos_token_id, ec.seed)
 
-    def _pages_from_budget(self, ec: EngineConfig, max_seq_len: int) -> int:
-        """Pool size from a byte budget: ``min(budget, 0.7 * free)`` over the
-        bytes of one page across every plane (engine/scheduler.py:100-103)."""
-        needs = [n for n in self.model.cache_needs() if n is not None and n.kind == "paged"]
-        esize = 4 if self.dtype == torch.float32 else 2
-        per_page = sum(2 * ec.kv_page_size * n.num_kv_heads * n.head_dim * esize for n in needs) or 1
-        free = torch.cuda.mem_get_info(self.device)[0]
-        budget = min(ec.kv_cache_budget_gb * 1e9, 0.7 * free)
-        cap = ec.scheduler.max_num_seqs * ((max_seq_len + ec.kv_page_size - 1) // ec.kv_page_size)
-        return max(16, min(int(budget // per_page), cap))
+    def _pages_per_group(self, ec: EngineConfig, max_seq_len: int) -> List[int]:
+        """Pool size of every cache group: ``ec.num_pages`` if given, else from the byte budget
+        ``min(budget, 0.7 * free)`` (engine/scheduler.py:100-103); see ``cache.manager.pool_sizes``."""
+        groups, _ = cache_groups(self.model)
+        budget = None
+        if not ec.num_pages:
+            budget = min(ec.kv_cache_budget_gb * 1e9, 0.7 * torch.cuda.mem_get_info(self.device)[0])
+        return pool_sizes(groups, ec.kv_page_size, 4 if self.dtype == torch.float32 else 2, max_seq_len,
+                          ec.scheduler.max_num_seqs, ec.scheduler.prefill_chunk, ec.num_pages, budget)
 
     # ---- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]],

@@ -34,24 +34,32 @@ _ERR_TEXT = {1: "token id outside the vocabulary", 2: "page id outside the pool"
              3: "position outside max_position_embeddings", 4: "a kernel's bounded wait ran out"}
 
 
+def cache_groups(model: DecoderModel):
+    """``(groups, where)`` of a model's cache planes (see ``plan_groups``)."""
+    return plan_groups(model.cache_needs(), [e.reads_cache_of for e in model.schedule])
+
+
 class ModelRunner:
-    def __init__(self, model: DecoderModel, device, dtype: torch.dtype, page_size: int, num_pages: int,
+    def __init__(self, model: DecoderModel, device, dtype: torch.dtype, page_size: int, num_pages,
                  max_seqs: int, max_seq_len: Optional[int] = None, use_cuda_graph: bool = False,
                  graph_batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)):
+        """``num_pages``: the pool size of every paged cache group, or one size per group (in the order
+        of ``cache_groups(model)``; entries of groups that are not paged are ignored): a group whose
+        layers see a window of keys needs far fewer pages than one that keeps them all."""
         if not torch.cuda.is_available():
             raise RuntimeError("prism_b200 needs a CUDA device; there is no CPU path")
         self.model, self.device, self.dtype = model, torch.device(device), dtype
         spec = model.spec
         self.max_positions = spec.max_positions
         self.max_seq_len = int(min(max_seq_len or spec.max_positions, spec.max_positions))
-        needs = model.cache_needs()
-        reads = [e.reads_cache_of for e in model.schedule]
-        self.groups, self.where = plan_groups(needs, reads)
+        self.groups, self.where = cache_groups(model)
         self.paged_groups = [g.index for g in self.groups if g.kind == "paged"]
-        self.cache = CacheManager(self.groups, page_size, num_pages, max_seqs, self.max_seq_len)
-        self.storage = CacheStorage(self.groups, self.where, page_size, [num_pages] * len(self.groups),
-                                    max_seqs, self.device, dtype)
-        self.pad_page = {g: num_pages for g in self.paged_groups}     # the scratch page
+        pages = [int(num_pages)] * len(self.groups) if isinstance(num_pages, int) else [int(n) for n in num_pages]
+        if len(pages) != len(self.groups):
+            raise ValueError(f"num_pages has {len(pages)} entries, the model has {len(self.groups)} cache groups")
+        self.cache = CacheManager(self.groups, page_size, pages, max_seqs, self.max_seq_len)
+        self.storage = CacheStorage(self.groups, self.where, page_size, pages, max_seqs, self.device, dtype)
+        self.pad_page = {g: pages[g] for g in self.paged_groups}      # each group's scratch page
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_cuda_graph = bool(use_cuda_graph)
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]

@@ -24,9 +24,9 @@ from ..config.model_config import read_config_json
 from ..model_registry import build_model
 from .pool import StaticWeightPool
 
-_ST_DTYPES = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16, "F64": torch.float64,
-              "I64": torch.int64, "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8,
-              "BOOL": torch.bool}
+_FLOAT_DTYPES = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16}
+_INT_DTYPES = {"I64": torch.int64, "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8}
+_ST_DTYPES = {**_FLOAT_DTYPES, **_INT_DTYPES}
 IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
 
 
@@ -79,7 +79,7 @@ def resolve_dtype(stored: List[str], compute_dtype: torch.dtype) -> torch.dtype:
         return torch.int32
     if compute_dtype == torch.float32:
         return torch.float32
-    return torch.float32 if any(d in (torch.float32, torch.float64) for d in dts) else torch.bfloat16
+    return torch.float32 if any(d == torch.float32 for d in dts) else torch.bfloat16
 
 
 def validate(named_params, header: Dict[str, Tuple[tuple, str]], allow_extra_head: bool = True):
@@ -98,8 +98,10 @@ def validate(named_params, header: Dict[str, Tuple[tuple, str]], allow_extra_hea
                 missing.append(s.name)
             elif tuple(header[s.name][0]) != tuple(s.shape):
                 wrong.append((s.name, header[s.name][0], s.shape))
-            elif header[s.name][1] not in _ST_DTYPES:
-                other.append(f"unsupported dtype {header[s.name][1]} for {s.name}")
+            elif header[s.name][1] not in (_INT_DTYPES if s.init == "table" else _FLOAT_DTYPES):
+                other.append(f"unsupported dtype {header[s.name][1]} for {s.name}: " +
+                             ("an integer table is stored as " + "/".join(_INT_DTYPES) if s.init == "table"
+                              else "weights are stored as " + "/".join(_FLOAT_DTYPES)))
         plan.append((qname, spec, True))
     unexpected = sorted(n for n in header if n not in wanted and not n.endswith(IGNORED_SUFFIXES))
     if missing or unexpected or wrong or other:
@@ -120,20 +122,37 @@ def load_weights(model, model_dir: str, device, compute_dtype: torch.dtype) -> S
     if dup:
         raise WeightError(other=[f"tensor stored in more than one shard: {', '.join(sorted(dup))}"])
     named = list(model.named_params())
-    tied = {spec.alias_of for _, spec in named if spec.alias_of}
-    # a tied head: the file's own head tensor, if any, is shadowed by the embedding
-    # (weight_manager.py:84-86 overwrites it with the alias)
-    shadowed = {s.name for _, spec in named if spec.alias_of and spec.optional for s in spec.sources}
-    for n in list(header):
-        if n in shadowed:
-            del header[n]
+    handles = {p: safe_open(p, framework="pt", device="cpu") for p in shards}
+    # A parameter tied to another one (the head to the embedding) has no tensor of its own.  If the
+    # file stores one all the same (exports often do), it must be the tied tensor over again; a file
+    # whose two tensors differ was not made for a tied model, and using either one would be a guess.
+    # (andre-fu/prism overwrites the file's tensor with the alias unseen, weight_manager.py:84-86.)
+    by_qname = dict(named)
+    differs = []
+    for qname, spec in named:
+        if not (spec.alias_of and spec.optional):
+            continue
+        target = by_qname[spec.alias_of]
+        for s, ts in zip(spec.sources, target.sources):
+            if s.name not in header:
+                continue
+            if ts.name in header and tuple(header[s.name][0]) == tuple(header[ts.name][0]):
+                a = handles[where[s.name]].get_tensor(s.name)
+                b = handles[where[ts.name]].get_tensor(ts.name)
+                if not torch.equal(a.float(), b.float()):
+                    differs.append(f"{s.name} is stored although it is tied to {ts.name}, and the two differ")
+            elif ts.name in header:
+                differs.append(f"{s.name} is stored although it is tied to {ts.name}, with another shape "
+                               f"({list(header[s.name][0])} against {list(header[ts.name][0])})")
+            del header[s.name]
+    if differs:
+        raise WeightError(other=differs)
     plan = validate(named, header)
     pool_plan = []
     for qname, spec, present in plan:
         dt = resolve_dtype([header[s.name][1] for s in spec.sources], compute_dtype) if present else None
         pool_plan.append((qname, spec, dt))
     pool = StaticWeightPool(pool_plan, device)
-    handles = {p: safe_open(p, framework="pt", device="cpu") for p in shards}
     for qname, spec, dt in pool_plan:
         if dt is None:
             continue

@@ -146,3 +146,30 @@ def test_random_orders_keep_the_invariants(seed, n_groups, page_size, num_pages)
     m.free_all()
     m.check_invariants()
     assert all(m.num_free_pages(g.index) == num_pages for g in groups if g.kind == "paged")
+
+
+def test_pool_sizes_per_group():
+    """A windowed group gets the pages its window and one portion need for every request slot, not the
+    pool of a group that keeps every key; a budget pays the windowed groups first."""
+    from prism_b200.cache.manager import pool_sizes
+    groups, _ = plan_groups([FULL, WIN, FULL, STATE, WIN], [None] * 5)
+    # explicit size: full groups get it, the windowed group ceil((20 + 16) / 8) + 1 = 6 pages for each of 4 slots
+    assert pool_sizes(groups, 8, 2, 128, 4, 16, num_pages=40) == [40, 24, 0]
+    assert pool_sizes(groups, 8, 2, 128, 4, 16, num_pages=10) == [10, 10, 0]        # never more than the others
+    # budget: bytes of a page = 2 (k, v) * planes * P * nkv * hd * element bytes
+    full_page = win_page = 2 * 2 * 8 * 2 * 16 * 2
+    budget = 24 * win_page + 30 * full_page + 5
+    assert pool_sizes(groups, 8, 2, 128, 4, 16, budget_bytes=budget) == [30, 24, 0]
+    assert pool_sizes(groups, 8, 2, 128, 4, 16, budget_bytes=1e12) == [64, 24, 0]      # cap: 4 requests of 128 tokens
+    assert pool_sizes(groups, 8, 2, 128, 4, 16, budget_bytes=0) == [16, 16, 0]         # floor (engine/scheduler.py:103)
+    # a windowed model runs any workload in that pool: portions of 16 tokens, 4 requests, long sequences
+    m = CacheManager(groups, 8, pool_sizes(groups, 8, 2, 128, 4, 16, num_pages=64), 4, 128)
+    for r in range(4):
+        m.add_request(r)
+    for _ in range(8):
+        for r in range(4):
+            assert m.can_append(r, 16)
+            m.append(r, 16)
+        for r in range(4):
+            m.commit(r, 16)
+        m.check_invariants()

@@ -146,7 +146,7 @@ def test_no_safetensors_and_no_config(tmp_path):
         load_model_folder(str(tmp_path), "cpu", torch.float32)
 
 
-def test_untied_model_rejects_missing_head_and_tied_ignores_extra_head(tmp_path):
+def test_untied_model_rejects_missing_head_and_tied_head_in_the_file_must_be_the_embedding(tmp_path):
     d = write_model_folder(TINY_B, 3, str(tmp_path / "b"))
     path = os.path.join(d, "model.safetensors")
     t = load_file(path)
@@ -156,10 +156,32 @@ def test_untied_model_rejects_missing_head_and_tied_ignores_extra_head(tmp_path)
         load_model_folder(d, "cpu", torch.float32)
     a = write_model_folder(TINY_A, 0, str(tmp_path / "a"))
     ta = load_file(os.path.join(a, "model.safetensors"))
-    ta["lm_head.weight"] = torch.zeros(256, 64)              # shadowed by the embedding, as in the reference
+    ta["lm_head.weight"] = ta["model.embed_tokens.weight"].clone()      # the embedding over again: accepted
     save_file(ta, os.path.join(a, "model.safetensors"))
     _, _, pool = load_model_folder(a, "cpu", torch.float32)
     assert pool["head.weight"].data_ptr() == pool["embedding.weight"].data_ptr()
+    ta["lm_head.weight"][3, 5] += 0.5                                   # one element off: not a tied model's file
+    save_file(ta, os.path.join(a, "model.safetensors"))
+    with pytest.raises(WeightError, match="lm_head.weight is stored although it is tied to model.embed_tokens.weight"):
+        load_model_folder(a, "cpu", torch.float32)
+    ta["lm_head.weight"] = torch.zeros(255, 64)
+    save_file(ta, os.path.join(a, "model.safetensors"))
+    with pytest.raises(WeightError, match="another shape"):
+        load_model_folder(a, "cpu", torch.float32)
+
+
+def test_dtypes_the_loader_refuses(tmp_path):
+    """Weights are bf16, fp16 or fp32 in the file; 64-bit floats and integers are an error, not a cast."""
+    d = write_model_folder(TINY_A, 0, str(tmp_path / "a"))
+    path = os.path.join(d, "model.safetensors")
+    t = load_file(path)
+    t["model.norm.weight"] = t["model.norm.weight"].double()
+    t["model.layers.0.mlp.down_proj.weight"] = t["model.layers.0.mlp.down_proj.weight"].to(torch.int32)
+    t["model.layers.1.mlp.down_proj.weight"] = t["model.layers.1.mlp.down_proj.weight"].half()      # fine
+    save_file(t, path)
+    with pytest.raises(WeightError) as e:
+        load_model_folder(d, "cpu", torch.bfloat16)
+    assert len(e.value.other) == 2 and "F64" in str(e.value) and "I32" in str(e.value)
 
 
 def test_random_weights_are_a_function_of_config_and_seed(tmp_path):
