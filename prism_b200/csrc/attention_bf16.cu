@@ -7,24 +7,19 @@ PRISM_EXPORT int prism_attention_bf16_supported(int hd, int nh, int nkv) {
 }
 
 // Decode: T tokens, one per request.  part_o: float [T, nh, nsplit, hd]; part_ml: float [T, nh, nsplit, 2].
-// counters (optional): T * nkv ints, zero before the first launch (the kernel leaves them zero): the splits are
-// then merged inside the kernel by the CTA that finishes last; without it a second kernel merges.
-// use_cluster (with counters null and 2 <= nsplit <= 8): the splits of a (token, kv head) run as one thread-block
-// cluster and merge through distributed shared memory; part_o / part_ml are then not touched.
+// With nsplit > 1 a second kernel merges the splits' partial results.
 PRISM_EXPORT int prism_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
                                              const void* kc, const void* vc, const int* block_table,
                                              int bt_width, const int* positions, const int* tok_seg,
                                              int T, int nh, int nkv, int hd, int page_size, int num_pages,
                                              int window, float scale, float* part_o, float* part_ml,
-                                             int nsplit, int* counters, int use_cluster, int* err,
-                                             cudaStream_t stream) {
+                                             int nsplit, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535 ||
-        (counters != nullptr && nsplit > 64))
+    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535)
         return (int)cudaErrorInvalidValue;
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
-             window, scale, part_o, part_ml, nsplit, err, stream, counters, use_cluster != 0
+             window, scale, part_o, part_ml, nsplit, err, stream
     return hd == 64 ? prism::launch_decode<64>(ARGS) : prism::launch_decode<128>(ARGS);
 #undef ARGS
 }
@@ -38,12 +33,12 @@ PRISM_EXPORT int prism_attention_decode_qkv_bf16(const float* parts, int ks, con
                                                  void* vc, const int* block_table, int bt_width, const int* positions,
                                                  const int* tok_seg, int T, int nh, int nkv, int hd, int page_size,
                                                  int num_pages, int window, float scale, float* part_o, float* part_ml,
-                                                 int nsplit, int* counters, int* err, cudaStream_t stream) {
+                                                 int nsplit, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535 || ks < 1 ||
         parts == nullptr || table == nullptr || ((uintptr_t)parts & 15) || ((uintptr_t)table & 15) ||
         ((uintptr_t)bias & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
-        (bias_dtype != PRISM_DTYPE_F32 && bias_dtype != PRISM_DTYPE_BF16) || (counters != nullptr && nsplit > 64))
+        (bias_dtype != PRISM_DTYPE_F32 && bias_dtype != PRISM_DTYPE_BF16))
         return (int)cudaErrorInvalidValue;
     prism::DecodeQKV f;
     f.D = (nh + 2 * nkv) * hd;
@@ -58,7 +53,7 @@ PRISM_EXPORT int prism_attention_decode_qkv_bf16(const float* parts, int ks, con
     f.max_pos = max_pos;
 #define ARGS (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
-             window, scale, part_o, part_ml, nsplit, err, stream, counters, false, &f
+             window, scale, part_o, part_ml, nsplit, err, stream, &f
     return hd == 64 ? prism::launch_decode<64>(ARGS) : prism::launch_decode<128>(ARGS);
 #undef ARGS
 }

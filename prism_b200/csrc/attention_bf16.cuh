@@ -4,8 +4,8 @@
 //    split of the keys); the nh/nkv query heads of that kv head form the rows
 //    of one 16-row MMA tile, so a K/V tile is read once for all of them.  Four
 //    warps each take 16 of a tile's 64 keys; partial (max, sum, output) of the
-//    warps are merged in shared memory, those of the splits by the CTA that
-//    finishes last (or, without a counter array, by a second small kernel).
+//    warps are merged in shared memory, those of the splits by a second small
+//    kernel.
 //  * prefill / portions: a CTA takes 64 query rows of one head of one
 //    segment; keys come from the request's pages (earlier portions and this
 //    one), causal with the portion's offset: the row at position p sees keys
@@ -18,8 +18,6 @@
 // through the block table with 16-byte cp.async (any page size) into padded
 // shared memory, 3 stages deep (decode) or double-buffered (prefill).
 #pragma once
-
-#include <cooperative_groups.h>
 
 #include "mma_helpers.cuh"
 
@@ -47,10 +45,6 @@ __device__ __forceinline__ float exp2_fast(float x, float m) {
 // ---------------------------------------------------------------------------
 // decode
 // ---------------------------------------------------------------------------
-// CLUSTER: the CTAs of one (token, kv head) - one per split - form a thread-block cluster and merge
-// their partial results through distributed shared memory: no partials in global memory, no second
-// kernel.  At most 8 splits (the portable cluster size).
-//
 // FUSED: the kernel takes over the back half of the qkv projection.  The projection of a few tokens
 // leaves float32 partial sums [ks, T, D] (D = (nh + 2 nkv) * HD, q | k | v); every CTA adds up, biases
 // and rotates the query rows of its kv head itself, and the CTA whose keys end at the token's own
@@ -109,7 +103,7 @@ __device__ __forceinline__ void rotate4(const float (&x1)[4], const float (&x2)[
     hi = make_uint2(pack_bf16(y2[0], y2[1]), pack_bf16(y2[2], y2[3]));
 }
 
-template <int HD, bool CLUSTER, bool FUSED = false>
+template <int HD, bool FUSED = false>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
@@ -117,9 +111,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh,
                    int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit,
-                   __nv_bfloat16* __restrict__ out, int out_stride, int* __restrict__ counters, int* err,
-                   const DecodeQKV fq) {
-    __shared__ int s_last;
+                   __nv_bfloat16* __restrict__ out, int out_stride, int* err, const DecodeQKV fq) {
     __shared__ __align__(16) __nv_bfloat16 s_own_kv[FUSED ? 2 * HD : 8];     // FUSED: this step's own key and value
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int SUB_ELEMS = 16 * STRIDE;                           // one warp's 16 keys of a tile
@@ -141,51 +133,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
     float* po = part_o + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * HD;   // + row * nsplit * HD
     float* pml = part_ml + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * 2;
-    // With `counters` the splits are merged here: every CTA leaves its partial result, and the CTA that
-    // arrives last at the (token, kv head) counter adds them up in split order and writes the output
-    // rows.  Nobody waits.  Without `counters` a second kernel merges.
-    auto merge_if_last = [&]() {
-        if (counters == nullptr) return;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            int* c = counters + (size_t)t * nkv + kvh;
-            const int old = atomicAdd(c, 1);
-            s_last = old == nsplit - 1;
-            if (s_last) *c = 0;                       // ready for the next launch
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        const float* bo = part_o + ((size_t)t * nh + (size_t)kvh * g) * nsplit * HD;
-        const float* bml = part_ml + ((size_t)t * nh + (size_t)kvh * g) * nsplit * 2;
-        // all (max, sum) pairs at once, then one weight per (row, split), then the weighted sums:
-        // two rounds of independent loads instead of a chain of dependent ones
-        float* sm = reinterpret_cast<float*>(KV);          // [g * nsplit] maxima, later weights
-        float* sl = sm + 16 * 64;                          // [g * nsplit] sums
-        for (int i = tid; i < g * nsplit; i += ATT_THREADS) {
-            sm[i] = __ldcg(bml + 2 * i);
-            sl[i] = __ldcg(bml + 2 * i + 1);
-        }
-        __syncthreads();
-        if (tid < g) {
-            float M = -INFINITY, L = 0.f;
-            for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, sm[tid * nsplit + sp]);
-            const float Mu = M == -INFINITY ? 0.f : M;
-            for (int sp = 0; sp < nsplit; ++sp) L += sl[tid * nsplit + sp] * exp2_guard(sm[tid * nsplit + sp], Mu);
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            for (int sp = 0; sp < nsplit; ++sp) sm[tid * nsplit + sp] = exp2_guard(sm[tid * nsplit + sp], Mu) * inv;
-        }
-        __syncthreads();
-        for (int i = tid; i < g * HD; i += ATT_THREADS) {
-            const int r = i / HD, d = i % HD;
-            float acc = 0.f;
-#pragma unroll 4
-            for (int sp = 0; sp < nsplit; ++sp) acc += __ldcg(bo + ((size_t)r * nsplit + sp) * HD + d) * sm[r * nsplit + sp];
-            out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(acc);
-        }
-    };
-    if (!CLUSTER && t0 >= t1) {           // nothing for this split: an empty partial
+    if (t0 >= t1) {                       // nothing for this split: an empty partial
         pdl_wait();
         for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * nsplit * HD + i % HD] = 0.f;
         for (int r = tid; r < g; r += ATT_THREADS) {
@@ -193,7 +141,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             pml[(size_t)r * nsplit * 2 + 1] = 0.f;
         }
         pdl_trigger_gemm();
-        merge_if_last();
         return;
     }
 
@@ -398,9 +345,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float* red_o = reinterpret_cast<float*>(KV);                 // [4][16][HD]
     float* red_m = red_o + 4 * 16 * HD;                          // [4][16]
     float* red_l = red_m + 4 * 16;                               // [4][16]
-    float* fin_o = red_l + 4 * 16;                               // [16][HD]  this split's merged partial (CLUSTER)
-    float* fin_m = fin_o + 16 * HD;                              // [16]
-    float* fin_l = fin_m + 16;                                   // [16]
     const int r0 = lane >> 2;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
@@ -427,10 +371,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             acc += red_o[((size_t)w * 16 + r) * HD + d] * f;
             L += red_l[w * 16 + r] * f;
         }
-        if (CLUSTER) {
-            fin_o[r * HD + d] = acc;
-            if (d == 0) { fin_m[r] = M; fin_l[r] = L; }
-        } else if (nsplit == 1) {
+        if (nsplit == 1) {
             // the only split: this is the result, no partial and no merge
             out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc * (1.f / L) : 0.f);
         } else {
@@ -441,46 +382,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             }
         }
     }
-    if (!CLUSTER) {
-        if (nsplit > 1) merge_if_last();
-        return;
-    }
-    // every split's (max, sum, output) is in its CTA's shared memory: each CTA of the cluster merges
-    // its share of the g * HD outputs, reading the others' partials through distributed shared memory
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    const int rank = (int)cluster.block_rank();
-    const int chunk = (g * HD + nsplit - 1) / nsplit;
-    const int i1 = min(g * HD, (rank + 1) * chunk);
-    for (int i = rank * chunk + tid; i < i1; i += ATT_THREADS) {
-        const int r = i / HD, d = i % HD;
-        float ms[8], ls[8], os[8];
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) {
-            if (sp < nsplit) {
-                const float* rm = cluster.map_shared_rank(fin_m, sp);
-                const float* rl = cluster.map_shared_rank(fin_l, sp);
-                const float* ro = cluster.map_shared_rank(fin_o, sp);
-                ms[sp] = rm[r]; ls[sp] = rl[r]; os[sp] = ro[r * HD + d];
-            } else {
-                ms[sp] = -INFINITY; ls[sp] = 0.f; os[sp] = 0.f;
-            }
-        }
-        float M = -INFINITY;
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, ms[sp]);
-        const float Mu = M == -INFINITY ? 0.f : M;
-        float L = 0.f, acc = 0.f;
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) {
-            const float f = exp2_guard(ms[sp], Mu);
-            L += ls[sp] * f;
-            acc += os[sp] * f;
-        }
-        out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-    }
-    cluster.sync();          // nobody leaves while its shared memory may still be read
 }
 
 // merge the splits: out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
@@ -698,38 +599,16 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
                   const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
                   int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
-                  int* err, cudaStream_t stream, int* counters = nullptr, bool use_cluster = false,
-                  const DecodeQKV* fused = nullptr) {
-    static_assert(dec_smem<HD>() >= (size_t)(5 * 16 * HD + 128 + 32) * sizeof(float) + 16 * TileRow<HD>::STRIDE * 2, "merge scratch must fit");
+                  int* err, cudaStream_t stream, const DecodeQKV* fused = nullptr) {
+    static_assert(dec_smem<HD>() >= (size_t)(4 * 16 * HD + 128) * sizeof(float), "merge scratch must fit");
     dim3 grid(nsplit, nkv, T);
-    if (counters == nullptr && use_cluster && nsplit >= 2 && nsplit <= 8) {
-        auto kc_ = attn_decode_kernel<HD, true>;
-        cudaFuncSetAttribute(kc_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(ATT_THREADS);
-        cfg.dynamicSmemBytes = dec_smem<HD>();
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = nsplit;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = pdl_enabled() ? 2 : 1;
-        return (int)cudaLaunchKernelEx(&cfg, kc_, q, q_stride, kc, vc, bt, bt_width, positions, tok_seg, nh, nkv, page_size,
-                                       page_shift_of(page_size), num_pages, window, scale * 1.4426950408889634f, part_o,
-                                       part_ml, nsplit, out, out_stride, (int*)nullptr, err, DecodeQKV());
-    }
-    auto kern = fused != nullptr ? attn_decode_kernel<HD, false, true> : attn_decode_kernel<HD, false>;
+    auto kern = fused != nullptr ? attn_decode_kernel<HD, true> : attn_decode_kernel<HD, false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
     cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
                                    positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
-                                   scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, counters, err,
+                                   scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, err,
                                    fused != nullptr ? *fused : DecodeQKV());
-    if (rc != cudaSuccess || counters != nullptr || nsplit == 1) return (int)rc;
+    if (rc != cudaSuccess || nsplit == 1) return (int)rc;
     return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD >= 128 ? 128 : 64), 0, stream,
                               (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);
 }

@@ -27,8 +27,6 @@
 // Every mbarrier wait is bounded (about two seconds): on expiry the kernel
 // records PRISM_ERR_WAIT_TIMEOUT, all roles fall through to the common exit,
 // tensor memory is released and the kernel returns.
-#include <cooperative_groups.h>
-
 #include "tcgen05.cuh"
 
 namespace prism {
@@ -37,22 +35,7 @@ namespace tc {
 constexpr int TILE_M = 128;          // weight rows per CTA tile (UMMA M)
 constexpr int THREADS = 192;         // 6 warps
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_QKV = 4 };
-
-// What the fused qkv epilogue (EPI_QKV) needs besides the product: where q goes, and how to rotate
-// and store k and v (the arguments of the rotary + cache-store kernel, csrc/rope_kv.cu).
-struct QkvArgs {
-    void* q_out;                  // bf16 [M, nh * hd]
-    int q_out_stride;
-    const int* positions;         // [M]
-    const int* tok_seg;           // [M]
-    const float2* table;          // [M, rotary_dim / 2] (cos, sin); null when rotary_dim == 0
-    int rotary_dim;
-    void* kc;                     // bf16 cache planes [pages, P, nkv, hd]; null: do not store
-    void* vc;
-    const int* block_table;
-    int bt_width, page_size, num_pages, nh, nkv, hd, max_pos;
-};
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
 
 template <int NTOK, int EPI> struct Cfg {
     static constexpr int W_TILES = EPI == EPI_SWIGLU ? 2 : 1;
@@ -67,8 +50,7 @@ template <int NTOK, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const void* __restrict__ bias, int bias_bf16, void* __restrict__ y, int ldy, int M, int N, int K,
-                 int kblocks_per_split, int pair_offset, float* __restrict__ ws, int* __restrict__ counters, int* err,
-                 const QkvArgs qa) {
+                 int kblocks_per_split, int pair_offset, float* __restrict__ ws, int* __restrict__ counters, int* err) {
     using C = Cfg<NTOK, EPI>;
     constexpr int W_TILES = C::W_TILES;
     constexpr int STAGES = C::STAGES;
@@ -80,7 +62,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
     __shared__ int abort_flag;
     __shared__ int is_last;
-    __shared__ long long s_slot[64];      // EPI_QKV: per token, element offset of its cache row (-1: do not store)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * TILE_M;                    // first weight row (output feature) of this tile
@@ -190,31 +171,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     for (int n = 0; n < NTOK; ++n) acc[w][n] = 0.f;
             }
             bool finish = true;
-            if (EPI == EPI_QKV) {
-                // this split's partial sums go to shared memory, token-major; the cluster's rank 0 finishes the tile
-                float* part = reinterpret_cast<float*>(tiles);
-#pragma unroll
-                for (int n = 0; n < NTOK; ++n) part[n * TILE_M + q * 32 + lane] = acc[0][n];
-                finish = false;
-                // rank 0 looks up every token's cache row now, in one round of independent loads,
-                // while the other splits are still finishing
-                const int n = q * 32 + lane;
-                if (blockIdx.y == 0 && n < NTOK) {
-                    long long slot = -1;
-                    if (n < M) {
-                        const int pos = qa.positions[n];
-                        if (pos < 0 || pos >= qa.max_pos) {
-                            report_error(err, PRISM_ERR_POSITION_RANGE);
-                            slot = -2;                         // nothing of this token is written
-                        } else if (qa.kc != nullptr) {
-                            const int page = qa.block_table[(size_t)qa.tok_seg[n] * qa.bt_width + pos / qa.page_size];
-                            if (page < 0 || page >= qa.num_pages) report_error(err, PRISM_ERR_PAGE_RANGE);
-                            else slot = ((long long)page * qa.page_size + pos % qa.page_size) * qa.nkv * qa.hd;
-                        }
-                    }
-                    s_slot[n] = slot;
-                }
-            }
             if ((EPI == EPI_BF16 || EPI == EPI_F32) && gridDim.y > 1) {
                 // K was split over gridDim.y CTAs: every CTA leaves its partial sums in the workspace and
                 // the one that arrives last at the tile's counter adds them up, in split order, and
@@ -262,58 +218,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             }
         }
     }
-    if (EPI == EPI_QKV) {
-        // The K-splits of this tile are one thread-block cluster.  Rank 0 adds their partial sums through
-        // distributed shared memory, adds the bias, rotates q and k (pairs j, j + rd/2 of a head sit in the
-        // same 128-row tile) and stores q to its buffer and k, v into the paged cache.
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();
-        if (cluster.block_rank() == 0 && warp >= 2 && abort_flag == 0) {
-            const int qd = warp & 3, mloc = qd * 32 + lane, f = m0 + mloc;
-            float* part = reinterpret_cast<float*>(tiles);
-            float* vals = part + NTOK * TILE_M;
-            const int nsp = (int)gridDim.y;
-            const float b = bias != nullptr && f < N ? load_param(bias, bias_bf16, f) : 0.f;
-            float v[NTOK];
-#pragma unroll
-            for (int n = 0; n < NTOK; ++n) v[n] = b;
-            for (int r = 0; r < nsp; ++r) {
-                const float* rp = cluster.map_shared_rank(part, r);
-#pragma unroll
-                for (int n = 0; n < NTOK; ++n) v[n] += rp[n * TILE_M + mloc];
-            }
-#pragma unroll
-            for (int n = 0; n < NTOK; ++n) vals[n * TILE_M + mloc] = v[n];
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int hd = qa.hd, q_size = qa.nh * hd, kv_size = qa.nkv * hd, half = qa.rotary_dim / 2;
-            const int region = f < q_size ? 0 : (f < q_size + kv_size ? 1 : 2);        // q, k, v
-            const int rf = f - (region == 0 ? 0 : (region == 1 ? q_size : q_size + kv_size));
-            const int head = rf / hd, j = rf % hd;
-            const bool rot = region != 2 && j < qa.rotary_dim;
-            const int partner = j < half ? mloc + half : mloc - half;
-            __nv_bfloat16* cache = reinterpret_cast<__nv_bfloat16*>(region == 1 ? qa.kc : qa.vc);
-            if (f < N) {
-#pragma unroll
-                for (int n = 0; n < NTOK; ++n) {
-                    if (n >= M) continue;
-                    const long long slot = s_slot[n];
-                    if (slot == -2) continue;
-                    float yv = v[n];
-                    if (rot) {
-                        const float2 cs = qa.table[(size_t)n * half + (j < half ? j : j - half)];
-                        const float xp = vals[n * TILE_M + partner];
-                        yv = j < half ? yv * cs.x - xp * cs.y : yv * cs.x + xp * cs.y;
-                    }
-                    if (region == 0)
-                        reinterpret_cast<__nv_bfloat16*>(qa.q_out)[(size_t)n * qa.q_out_stride + f] = __float2bfloat16_rn(yv);
-                    else if (cache != nullptr && slot >= 0)
-                        cache[slot + (long long)head * hd + j] = __float2bfloat16_rn(yv);
-                }
-            }
-        }
-        cluster.sync();          // the other ranks' partial sums stay alive until rank 0 has read them
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0 && abort_flag) report_error(err, PRISM_ERR_WAIT_TIMEOUT);
@@ -341,39 +245,7 @@ int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, con
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
     dim3 grid((N + TILE_M - 1) / TILE_M, ksplit);
     return (int)launch_kernel(kern, grid, dim3(THREADS), C::SMEM, stream, mw, mx, bias, bias_bf16, y, ldy, M, N, K, per,
-                              pair_offset, ws, counters, err, QkvArgs{});
-}
-
-// The qkv projection with the fused epilogue: grid (tiles, ksplit), clusters of (1, ksplit, 1).
-template <int NTOK>
-int launch_qkv(const void* W, int ldw, const void* x, int ldx, const void* bias, int bias_bf16, int M, int N, int K,
-               int ksplit, const QkvArgs& qa, int* err, cudaStream_t stream) {
-    using C = Cfg<NTOK, EPI_QKV>;
-    CUtensorMap mw, mx;
-    int rc = make_map(&mw, W, N, K, ldw, TILE_M);
-    if (rc) return rc;
-    rc = make_map(&mx, x, M, K, ldx, NTOK);
-    if (rc) return rc;
-    const int total_kb = (K + TILE_K - 1) / TILE_K;
-    const int per = (total_kb + ksplit - 1) / ksplit;
-    auto kern = gemm_swap_kernel<NTOK, EPI_QKV>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + TILE_M - 1) / TILE_M, ksplit);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = C::SMEM;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = ksplit;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, kern, mw, mx, bias, bias_bf16, (void*)nullptr, 0, M, N, K, per, 0,
-                                   (float*)nullptr, (int*)nullptr, err, qa);
+                              pair_offset, ws, counters, err);
 }
 
 }  // namespace tc
@@ -383,33 +255,6 @@ int launch_qkv(const void* W, int ldw, const void* x, int ldx, const void* bias,
 PRISM_EXPORT int prism_set_pdl(int on) {
     prism::pdl_enabled() = on ? 1 : 0;
     return prism::pdl_enabled();
-}
-
-// 1 if the fused qkv projection (bias + rotary + cache store in the GEMM's epilogue) takes these sizes
-PRISM_EXPORT int prism_gemm_tcgen05_qkv_supported(int M, int K, int nh, int nkv, int hd, int rotary_dim) {
-    return M >= 1 && M <= 16 && K >= 8 && K % 8 == 0 && (hd == 64 || hd == 128) && (nh * hd) % 128 == 0 &&
-           (nkv * hd) % 128 == 0 && rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0;
-}
-
-// q/k/v projection of up to 16 tokens with everything up to the cache store in one kernel:
-// W [(nh + 2 nkv) * hd, K], x [M, K], bias optional; K split over `ksplit` (1..8) CTAs that form a cluster.
-PRISM_EXPORT int prism_gemm_tcgen05_qkv(const void* W, int ldw, const void* x, int ldx, const void* bias, int bias_dtype,
-                                        int M, int K, int ksplit, void* q_out, int q_out_stride, const int* positions,
-                                        const int* tok_seg, const float* table, int rotary_dim, void* kc, void* vc,
-                                        const int* block_table, int bt_width, int page_size, int num_pages, int nh,
-                                        int nkv, int hd, int max_pos, int* err, cudaStream_t stream) {
-    using namespace prism::tc;
-    if (M <= 0) return 0;
-    if (!prism_gemm_tcgen05_qkv_supported(M, K, nh, nkv, hd, rotary_dim) || ldw % 8 || ldx % 8 || ksplit < 1 || ksplit > 8 ||
-        ((uintptr_t)W & 15) || ((uintptr_t)x & 15) || (rotary_dim > 0 && table == nullptr))
-        return (int)cudaErrorInvalidValue;
-    QkvArgs qa;
-    qa.q_out = q_out; qa.q_out_stride = q_out_stride; qa.positions = positions; qa.tok_seg = tok_seg;
-    qa.table = reinterpret_cast<const float2*>(table); qa.rotary_dim = rotary_dim; qa.kc = kc; qa.vc = vc;
-    qa.block_table = block_table; qa.bt_width = bt_width; qa.page_size = page_size; qa.num_pages = num_pages;
-    qa.nh = nh; qa.nkv = nkv; qa.hd = hd; qa.max_pos = max_pos;
-    return launch_qkv<16>(W, ldw, x, ldx, bias, bias_dtype == PRISM_DTYPE_BF16, M, (nh + 2 * nkv) * hd, K, ksplit, qa, err,
-                          stream);
 }
 
 // 1 if the kernel takes these sizes: up to 64 tokens, K a multiple of 8 (16-byte rows for TMA).

@@ -91,9 +91,9 @@ class _Sig:
                                _i, _f, _p, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
-                                   _p, _p, _i, _p, _i, _p, _p]
+                                   _p, _p, _i, _p, _p]
     prism_attention_decode_qkv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
-                                       _i, _f, _p, _p, _i, _p, _p, _p]
+                                       _i, _f, _p, _p, _i, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
     prism_attention_prefill_tc_supported = [_i, _i, _i, _i]
@@ -106,9 +106,6 @@ class _Sig:
     prism_argmax_split = [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_set_pdl = [_i]
     prism_gemm_tcgen05_supported = [_i, _i, _i]
-    prism_gemm_tcgen05_qkv_supported = [_i, _i, _i, _i, _i, _i]
-    prism_gemm_tcgen05_qkv = [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i,
-                              _i, _i, _p, _p]
     prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]
     prism_gemv_bf16_supported = [_i, _i, _i]
     prism_gemv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]
@@ -187,9 +184,6 @@ def sgemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: t
 
 
 USE_GEMV = os.environ.get("PRISM_GEMV", "1") != "0"
-# the plain (bias) epilogue is slower than the library product at most decode shapes on B200 and is
-# opt-in; the paired-SwiGLU epilogue saves the [M, 2I] round trip and a launch and is the default
-USE_GEMV_PLAIN = os.environ.get("PRISM_GEMV_PLAIN", "0") == "1"
 GEMV_MAX_M = int(os.environ.get("PRISM_GEMV_MAX_M", "16"))      # above 16 tokens it streams at half the bandwidth
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 
@@ -228,16 +222,22 @@ def _tc_err_word(device) -> torch.Tensor:
 
 
 _tc_ws = {}
+_tc_ws_retired = []       # outgrown workspaces: never freed, a captured graph may still hold their addresses
 
 
 def _tc_workspace(device, floats: int, tiles: int):
     """Split-K workspace of the tensor-core GEMM: partial sums and one counter per
-    tile.  Grown outside graph capture only; kernels leave the counters at zero."""
+    tile.  Grown outside graph capture only; kernels leave the counters at zero.
+    A workspace that a later call outgrows is kept alive for the life of the process:
+    decode graphs captured earlier replay with its addresses, and memory given back to
+    the allocator could by then hold somebody's activations."""
     key = torch.device(device).index or 0
     ws = _tc_ws.get(key)
     if ws is None or ws[0].numel() < floats or ws[1].numel() < tiles:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("the split-K workspace must be sized before graph capture (run one step eagerly first)")
+        if ws is not None:
+            _tc_ws_retired.append(ws)
         ws = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
               torch.zeros(max(tiles, 4096), dtype=torch.int32, device=device))
         _tc_ws[key] = ws
@@ -296,13 +296,13 @@ def tc_gemm_ok(x: torch.Tensor, w: torch.Tensor, max_m: Optional[int] = None) ->
             and bool(lib().prism_gemm_tcgen05_supported(M, w.shape[0], K)))
 
 
-def tc_ksplit(N: int, K: int) -> int:
-    """CTAs that share one 128-row tile's K range: about one CTA per SM in all,
-    at least 8 blocks of 64 k each."""
+def tc_ksplit(N: int, K: int, sms: Optional[int] = None) -> int:
+    """CTAs that share one 128-row tile's K range: about one CTA per SM in all (``sms``: the device's
+    count), at least 8 blocks of 64 k each."""
     tiles = (N + 127) // 128
     if TC_KSPLIT_FORCED:
         return TC_KSPLIT_FORCED
-    return max(1, min(NUM_SMS // tiles, ((K + 63) // 64) // 8))
+    return max(1, min((sms or num_sms()) // tiles, ((K + 63) // 64) // 8))
 
 
 def check_tc_errors():
@@ -354,13 +354,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         if out is None or out.dtype != want:
             out = torch.empty((M, N), dtype=want, device=x.device)
         gemm_tc(x, w, bias, out, EPI_F32 if want == torch.float32 else EPI_BF16, ksplit=tc_ksplit(N, x.shape[1]))
-        return out
-    if USE_GEMV_PLAIN and want in (torch.float32, torch.bfloat16) and M <= GEMV_MAX_M and x.stride(-1) == 1 \
-            and (out is None or out.stride(-1) == 1) and gemv_supported(M, N, x.shape[1]) \
-            and (M == 1 or x.stride(0) % 8 == 0):
-        if out is None or out.dtype != want:
-            out = torch.empty((M, N), dtype=want, device=x.device)
-        gemv(x, w, bias, out, EPI_F32 if want == torch.float32 else EPI_BF16)
         return out
     # bf16 x bf16, library product with float32 accumulation
     if want == torch.float32:
@@ -446,41 +439,10 @@ def rope_kv_write_partial(parts: torch.Tensor, bias: Optional[torch.Tensor], q_o
            "rope_kv_write_partial")
 
 
-# The qkv projection of a few tokens.  Default: K-split tcgen05 GEMM -> float32 partial sums -> one kernel that
-# adds them and the bias, rotates and stores (several CTAs per token).  PRISM_QKV_FUSED=1: all of it in the GEMM's
-# epilogue, the K-split CTAs as a cluster (one launch fewer, but the epilogue of 36 clusters is slower than the
-# separate kernel's 64 CTAs: 3.15 against 3.10 ms a step at batch 8).  PRISM_QKV_LIBRARY=1 (with PRISM_QKV_PARTIAL=0):
-# the library product and the rotary kernel, for comparison.
-QKV_FUSED = os.environ.get("PRISM_QKV_FUSED", "0") == "1"
+# The qkv projection of a few tokens: K-split tcgen05 GEMM -> float32 partial sums -> one kernel that adds them and
+# the bias, rotates and stores (several CTAs per token).  PRISM_QKV_LIBRARY=1 (with PRISM_QKV_PARTIAL=0): the
+# library product and the rotary kernel, for comparison.
 QKV_LIBRARY = os.environ.get("PRISM_QKV_LIBRARY", "0") == "1"
-
-
-def gemm_tc_qkv(x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], q_out: torch.Tensor,
-                positions: torch.Tensor, tok_seg: torch.Tensor, table: Optional[torch.Tensor], rotary_dim: int,
-                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                block_table: Optional[torch.Tensor], num_pages: int, max_pos: int, nkv: int, ksplit: int,
-                err: torch.Tensor):
-    """The qkv projection of up to 16 tokens on the tensor-core GEMM with bias,
-    rotary encoding and the cache store in its epilogue: the K-splits of a
-    128-row tile form a thread-block cluster, exchange their partial sums through
-    distributed shared memory, and rank 0 writes q ``[T, nh, hd]`` and k, v."""
-    _cuda(x, qkv_w, qkv_b, q_out, positions, tok_seg, table, k_cache, v_cache, block_table)
-    M, K = x.shape
-    _, nh, hd = q_out.shape
-    assert qkv_w.shape == ((nh + 2 * nkv) * hd, K) and q_out.is_contiguous() and q_out.dtype == torch.bfloat16
-    assert x.dtype == torch.bfloat16 and qkv_w.dtype == torch.bfloat16 and x.stride(1) == 1 and qkv_w.stride(1) == 1
-    P = W = 0
-    if k_cache is not None:
-        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == torch.bfloat16
-        assert k_cache.shape[2:] == (nkv, hd)
-        P, W = k_cache.shape[1], block_table.shape[1]
-    if rotary_dim:
-        assert table.dtype == torch.float32 and table.shape == (M, rotary_dim // 2, 2)
-    _check(lib().prism_gemm_tcgen05_qkv(_ptr(qkv_w), qkv_w.stride(0), _ptr(x), x.stride(0) if M > 1 else K, _ptr(qkv_b),
-                                        F32 if qkv_b is None else _dt(qkv_b), M, K, int(ksplit), _ptr(q_out), nh * hd,
-                                        _ptr(positions), _ptr(tok_seg), _ptr(table), rotary_dim, _ptr(k_cache),
-                                        _ptr(v_cache), _ptr(block_table), W, P, num_pages, nh, nkv, hd, max_pos,
-                                        _ptr(err), _stream()), "gemm_tcgen05_qkv")
 
 
 def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[torch.Tensor], nh: int, nkv: int,
@@ -501,13 +463,6 @@ def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[
             rope_table(ctx.positions, rot.inv_freq, table)
     kc, vc = (cache.k, cache.v) if cache.write else (None, None)
     rd = rot.rotary_dim if rot is not None else 0
-    if QKV_FUSED and tc_gemm_ok(x, qkv_w) and (rd == 0 or table is not None) and \
-            lib().prism_gemm_tcgen05_qkv_supported(T, x.shape[1], nh, nkv, hd, rd):
-        q = ctx.alloc((T, nh, hd), x.dtype)
-        ks = min(8, tc_ksplit(qkv_w.shape[0], qkv_w.shape[1]))
-        gemm_tc_qkv(x, qkv_w, qkv_b, q, ctx.positions, ctx.tok_seg, table, rd, kc, vc, cache.block_table,
-                    cache.num_pages, ctx.max_positions, nkv, ks, ctx.err)
-        return q
     if QKV_PARTIAL and table is not None and tc_gemm_ok(x, qkv_w) and hd % 8 == 0 and rot.rotary_dim % 16 == 0:
         ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
         if ks > 1:
@@ -589,36 +544,29 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optiona
 # composites: the places where a faster kernel is chosen for a shape
 # --------------------------------------------------------------------------
 
-NUM_SMS = 148
+_num_sms = {}
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (default: the current CUDA device), asked of the driver
+    once per device.  The grid shapes below (K-splits, attention splits) are sized by it."""
+    if not torch.cuda.is_available():
+        raise KernelError("the number of SMs is a property of a CUDA device; pass sms= to size a grid without one")
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    n = _num_sms.get(idx)
+    if n is None:
+        n = _num_sms[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return n
+
+
 FORCE_GENERIC_ATTENTION = os.environ.get("PRISM_ATTENTION", "") == "generic"
 
 
-_attn_counters = {}
-
-
-def _decode_counters(device, n: int) -> torch.Tensor:
-    """Per-(token, kv head) arrival counters of the decode attention; zero between launches."""
-    key = torch.device(device).index or 0
-    c = _attn_counters.get(key)
-    if c is None or c.numel() < n:
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the attention counters must be sized before graph capture (run one step eagerly first)")
-        c = _attn_counters[key] = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
-    return c
-
-
-# merging the splits inside the attention kernel (last CTA) measured slower on B200 than a second small
-# kernel launched with programmatic dependent launch; it stays available and tested
-FUSED_MERGE = os.environ.get("PRISM_ATTN_FUSED_MERGE", "0") == "1"
-# merging the splits through distributed shared memory in a thread-block cluster: correct and tested, but
-# measured slightly slower at decode sizes than partials + a merge kernel under programmatic dependent launch
-CLUSTER_MERGE = os.environ.get("PRISM_ATTN_CLUSTER", "0") == "1"
 QKV_PARTIAL = os.environ.get("PRISM_QKV_PARTIAL", "1") != "0"
 
 
 def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
-                          scale, nsplit, part_o, part_ml, err, fused_merge: Optional[bool] = None,
-                          cluster: Optional[bool] = None):
+                          scale, nsplit, part_o, part_ml, err):
     """Tensor-core decode attention (one token per request) with the keys split
     over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
     ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results."""
@@ -629,23 +577,18 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
     assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1
     assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
-    fused_merge = FUSED_MERGE if fused_merge is None else fused_merge
-    cluster = CLUSTER_MERGE if cluster is None else cluster
-    cluster = bool(cluster) and not fused_merge and 2 <= nsplit <= 8
     _check(lib().prism_attention_decode_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache),
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                              _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                              int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                             int(nsplit), _ptr(_decode_counters(q.device, T * nkv)) if fused_merge else None,
-                                             int(cluster), _ptr(err), _stream()), "attention_decode_bf16")
-    if not fused_merge and not cluster:
+                                             int(nsplit), _ptr(err), _stream()), "attention_decode_bf16")
+    if nsplit > 1:
         global launch_count
         launch_count += 1          # the merge kernel
 
 
 def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache, block_table, positions, tok_seg,
-                              num_pages, nh, window, scale, nsplit, part_o, part_ml, err,
-                              fused_merge: Optional[bool] = None):
+                              num_pages, nh, window, scale, nsplit, part_o, part_ml, err):
     """Decode attention that finishes the qkv projection itself: ``parts [ks, T, (nh + 2 nkv) * hd]`` are the
     projection's float32 partial sums, ``bias`` its bias or None, ``table [T, hd / 2, 2]`` the step's cos/sin.
     Every CTA adds, biases and rotates the query rows it needs; the CTA that holds a token's own position
@@ -660,15 +603,13 @@ def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (T, nh * hd)
     assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
-    fused_merge = FUSED_MERGE if fused_merge is None else fused_merge
     _check(lib().prism_attention_decode_qkv_bf16(_ptr(parts), ks, _ptr(bias), F32 if bias is None else _dt(bias),
                                                  _ptr(table), int(max_pos), _ptr(out), out.stride(0), _ptr(k_cache),
                                                  _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                                  _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                                  int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                                 int(nsplit), _ptr(_decode_counters(out.device, T * nkv)) if fused_merge else None,
-                                                 _ptr(err), _stream()), "attention_decode_qkv_bf16")
-    if not fused_merge and nsplit > 1:
+                                                 int(nsplit), _ptr(err), _stream()), "attention_decode_qkv_bf16")
+    if nsplit > 1:
         global launch_count
         launch_count += 1          # the merge kernel
 
@@ -695,7 +636,8 @@ PREFILL_SPLIT_FROM_TILES = 64     # fewer key tiles than this are not split: the
 PREFILL_SPLIT_FROM_TILES_FEW_CTAS = 32    # ... unless the query tiles fill under a quarter of the GPU
 
 
-def prefill_splits(S: int, max_q_len: int, nh: int, max_kv_len: int, window: Optional[int]) -> int:
+def prefill_splits(S: int, max_q_len: int, nh: int, max_kv_len: int, window: Optional[int],
+                   sms: Optional[int] = None) -> int:
     """CTAs that share the key tiles of one (head, 128 query rows) in the tcgen05 prefill kernel: 1 unless
     the query tiles alone leave most of the GPU idle and the keys are many (a short portion against a
     long cache); then as many as fill the two CTAs per SM, each with at least PREFILL_SPLIT_MIN_TILES.
@@ -703,6 +645,7 @@ def prefill_splits(S: int, max_q_len: int, nh: int, max_kv_len: int, window: Opt
     127 -> 46 us in 8, 32,768 cached 471 -> 86 us in 10; 512 new tokens after 2,048: 48 us whole, 55 us in 2.)"""
     if os.environ.get("PRISM_PREFILL_SPLITS"):
         return int(os.environ["PRISM_PREFILL_SPLITS"])
+    NUM_SMS = sms or num_sms()
     ctas = S * nh * ((max_q_len + 127) // 128)
     span = min(max_kv_len, window + max_q_len) if window else max_kv_len
     tiles = (span + 63) // 64
@@ -787,7 +730,8 @@ DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what t
                                     # 203 -> 201 us in 4 splits, 32,768 keys 717 -> 673 us)
 
 
-def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int], balance: bool = True) -> int:
+def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int], balance: bool = True,
+                  sms: Optional[int] = None) -> int:
     """How many CTAs share one (token, kv head)'s keys: as many as fill one wave
     of two CTAs per SM, at most one per 64-key tile.  More, shorter CTAs lose:
     each pays the same fixed latencies (position, block table, first bytes, merge).  ``max_kv_len`` is the
@@ -796,6 +740,7 @@ def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int], bala
     of 32,768 says nothing about the contexts a replay will meet."""
     if os.environ.get("PRISM_DECODE_SPLITS"):
         return int(os.environ["PRISM_DECODE_SPLITS"])
+    NUM_SMS = sms or num_sms()
     span = min(max_kv_len, window + 64) if window else max_kv_len
     tiles = max(1, (span + 63) // 64)
     fill = (2 * NUM_SMS) // max(1, T * nkv)
@@ -813,8 +758,6 @@ def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int], bala
                 break
             if balance(k) >= 0.95:
                 return k
-    if CLUSTER_MERGE and 8 < n <= 12:
-        n = 8                                         # one cluster of 8 rather than a few more splits through memory
     return n
 
 
@@ -899,9 +842,9 @@ def qkv_attention(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[tor
     ``qkv_rotate_store`` followed by ``attention``; with ``QKV_IN_ATTENTION`` a pure decode step of a few
     tokens runs as two kernels (K-split projection, attention that finishes the projection)."""
     T = x.shape[0]
-    if (QKV_IN_ATTENTION and QKV_PARTIAL and not QKV_FUSED and ctx.decode_only and cache.write and rot is not None
+    if (QKV_IN_ATTENTION and QKV_PARTIAL and ctx.decode_only and cache.write and rot is not None
             and rot.rotary_dim == hd and x.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
-            and not FORCE_GENERIC_ATTENTION and not CLUSTER_MERGE and tc_gemm_ok(x, qkv_w)
+            and not FORCE_GENERIC_ATTENTION and tc_gemm_ok(x, qkv_w)
             and cache.k.is_contiguous() and cache.v.is_contiguous() and attention_bf16_supported(hd, nh, nkv)):
         ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
         if ks > 1:

@@ -1,33 +1,51 @@
 """How many CTAs share the keys of a query tile (prefill) or of a (token, kv head) (decode): the
 host-side choices of ``prism_b200.ops``, which need no GPU."""
 
+import pytest
+
 from prism_b200 import ops
+
+B200 = 148        # SMs of the device the measured thresholds come from; the tests size the grids for it by hand
 
 
 def test_prefill_splits_choice():
     """Splits only when the query tiles leave the GPU idle and the keys are many."""
-    assert ops.prefill_splits(1, 2048, 28, 2048, None) == 1          # 448 CTAs already
-    assert ops.prefill_splits(1, 128, 28, 640, None) == 1            # 10 key tiles: not worth a merge
-    assert ops.prefill_splits(1, 128, 28, 2048 + 128, None) == 2     # few CTAs: worth it from 2,048 keys
-    assert ops.prefill_splits(1, 512, 28, 2048 + 512, None) == 1
-    n = ops.prefill_splits(1, 128, 28, 32768 + 128, None)
-    assert 2 <= n <= 16 and 28 * n <= 2 * ops.NUM_SMS
-    assert ops.prefill_splits(1, 128, 28, 32768 + 128, 512) == 1     # a window of 512 keys: few tiles
-    assert ops.prefill_splits(4, 256, 28, 32768, None) == 1
+    assert ops.prefill_splits(1, 2048, 28, 2048, None, sms=B200) == 1          # 448 CTAs already
+    assert ops.prefill_splits(1, 128, 28, 640, None, sms=B200) == 1            # 10 key tiles: not worth a merge
+    assert ops.prefill_splits(1, 128, 28, 2048 + 128, None, sms=B200) == 2     # few CTAs: worth it from 2,048 keys
+    assert ops.prefill_splits(1, 512, 28, 2048 + 512, None, sms=B200) == 1
+    n = ops.prefill_splits(1, 128, 28, 32768 + 128, None, sms=B200)
+    assert 2 <= n <= 16 and 28 * n <= 2 * B200
+    assert ops.prefill_splits(1, 128, 28, 32768 + 128, 512, sms=B200) == 1     # a window of 512 keys: few tiles
+    assert ops.prefill_splits(4, 256, 28, 32768, None, sms=B200) == 1
 
 
 def test_decode_splits_choice():
     """As many splits as fill one wave; a batch that fills the GPU unevenly gets a few splits once the
     contexts are long enough to pay for the merge."""
-    assert ops.decode_splits(8, 4, 2100, None) == 9                  # 288 CTAs for 296 places
-    assert ops.decode_splits(1, 4, 2100, None) == 33                 # one per 64-key tile
-    assert ops.decode_splits(64, 4, 2100, None) == 1                 # short contexts: no merge
-    assert ops.decode_splits(64, 4, 8192, None) == 1
-    assert ops.decode_splits(64, 4, 32768, None) == 4                # 256 CTAs would be 2 + 1 per SM
-    assert ops.decode_splits(74, 4, 32768, None) == 1                # 296 CTAs: even already
-    assert ops.decode_splits(64, 4, 32768, 512) == 1                 # a window of 512 keys is a short context
-    assert ops.decode_splits(64, 4, 32768, None, balance=False) == 1     # a captured graph knows a bound only
-    assert ops.decode_splits(8, 4, 32768, None, balance=False) == 9
+    assert ops.decode_splits(8, 4, 2100, None, sms=B200) == 9                  # 288 CTAs for 296 places
+    assert ops.decode_splits(1, 4, 2100, None, sms=B200) == 33                 # one per 64-key tile
+    assert ops.decode_splits(64, 4, 2100, None, sms=B200) == 1                 # short contexts: no merge
+    assert ops.decode_splits(64, 4, 8192, None, sms=B200) == 1
+    assert ops.decode_splits(64, 4, 32768, None, sms=B200) == 4                # 256 CTAs would be 2 + 1 per SM
+    assert ops.decode_splits(74, 4, 32768, None, sms=B200) == 1                # 296 CTAs: even already
+    assert ops.decode_splits(64, 4, 32768, 512, sms=B200) == 1                 # a window of 512 keys is a short context
+    assert ops.decode_splits(64, 4, 32768, None, balance=False, sms=B200) == 1     # a captured graph knows a bound only
+    assert ops.decode_splits(8, 4, 32768, None, balance=False, sms=B200) == 9
+
+
+def test_grids_follow_the_device():
+    """The SM count is the device's, not a constant: other counts give other grids, and without a
+    device the count must be given."""
+    assert ops.decode_splits(8, 4, 2100, None, sms=132) == 8         # 256 CTAs for 264 places
+    assert ops.decode_splits(8, 4, 2100, None, sms=64) == 4
+    assert ops.tc_ksplit(4608, 3584, sms=148) == 4 and ops.tc_ksplit(4608, 3584, sms=80) == 2
+    assert ops.tc_ksplit(3584, 18944, sms=148) == 5 and ops.tc_ksplit(152064, 3584, sms=148) == 1
+    assert ops.prefill_splits(1, 128, 28, 32768 + 128, None, sms=64) < ops.prefill_splits(1, 128, 28, 32768 + 128, None, sms=148)
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(ops.KernelError, match="sms="):
+            ops.decode_splits(8, 4, 2100, None)
 
 
 def test_prefill_kernel_choice():

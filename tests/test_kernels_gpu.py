@@ -251,6 +251,41 @@ def test_gemm_tcgen05(M, N, K):
     assert int(err) == 0
 
 
+def test_split_k_workspace_outgrown_after_a_graph_was_captured():
+    """A graph captured with the K-split product's workspace keeps replaying correctly after a later eager
+    call has outgrown that workspace: the old one stays allocated, so nobody else's data can land where the
+    graph still writes its partial sums and counts its arrivals."""
+    ops = _ops()
+    N, K, ks = 3584, 3584, 5
+    w = _rand((N, K), torch.bfloat16, 70, 0.05)
+    b = _rand((N,), torch.bfloat16, 71)
+    x8, x64 = _rand((8, K), torch.bfloat16, 72), _rand((64, K), torch.bfloat16, 73)
+    ref8 = x8.float() @ w.float().T + b.float()
+    ops._tc_ws.clear()                                        # start from the initial size, as a fresh process does
+    out8 = torch.empty(8, N, dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x8, w, b, out8, ops.EPI_F32, ksplit=ks)      # sizes the workspace (1 Mi floats) before capture
+    first = ops._tc_ws[0][0]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        ops.gemm_tc(x8, w, b, out8, ops.EPI_F32, ksplit=ks)
+    torch.cuda.synchronize()
+    out64 = torch.empty(64, N, dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x64, w, b, out64, ops.EPI_F32, ksplit=ks)    # 5 * 64 * 3584 floats: more than the first workspace
+    assert ops._tc_ws[0][0].numel() > first.numel() and ops._tc_ws[0][0].data_ptr() != first.data_ptr()
+    del first
+    # whatever the allocator hands out now must not be the graph's workspace
+    junk = [torch.full((1 << 20,), float("nan"), device=DEV) for _ in range(8)]
+    out8.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    scale = float(ref8.abs().max())
+    assert torch.allclose(out8, ref8, atol=2e-3 * scale, rtol=2e-3)
+    assert all(bool(torch.isnan(j).all()) for j in junk), "the replay wrote into memory that was given away"
+    assert torch.allclose(out64, x64.float() @ w.float().T + b.float(), atol=2e-3 * scale, rtol=2e-3)
+
+
 @pytest.mark.parametrize("T,I", [(3, 100), (40, 18944)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu(T, I, dtype):
@@ -365,51 +400,6 @@ def test_rope_kv_write_from_partial_sums(nh, nkv, hd, rd, P, dtype, with_bias):
         assert torch.allclose(vc[page, p_ % P].float(), tv[t], atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("nh,nkv,hd,rd,P,K", [(28, 4, 128, 128, 256, 3584), (6, 2, 64, 64, 16, 136), (4, 2, 64, 32, 8, 200),
-                                              (2, 1, 128, 0, 16, 96)])
-@pytest.mark.parametrize("M", [1, 8, 16])
-@pytest.mark.parametrize("ksplit", [1, 2, 4])
-def test_fused_qkv_projection_rotary_store(nh, nkv, hd, rd, P, K, M, ksplit):
-    """The qkv GEMM with bias, rotary encoding and cache store in its epilogue
-    (cluster of K-splits) against: float32 product, float32 rotation, one rounding."""
-    ops = _ops()
-    D = (nh + 2 * nkv) * hd
-    x = _rand((M, K), torch.bfloat16, 60)
-    w = _rand((D, K), torch.bfloat16, 61, 0.05)
-    bias = _rand((D,), torch.bfloat16, 62)
-    W = 12
-    positions = torch.tensor([(37 * i + 5) % (W * P) for i in range(M)], dtype=torch.int32, device=DEV)
-    tok_seg = torch.arange(M, dtype=torch.int32, device=DEV)
-    pages = M * W
-    bt = torch.arange(pages, dtype=torch.int32, device=DEV).view(M, W)
-    table = None
-    inv = None
-    if rd:
-        inv = (1.0 / (1e4 ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))).to(DEV)
-        table = torch.empty(M, rd // 2, 2, dtype=torch.float32, device=DEV)
-        ops.rope_table(positions, inv, table)
-    kc = torch.zeros(pages, P, nkv, hd, dtype=torch.bfloat16, device=DEV)
-    vc = torch.zeros_like(kc)
-    q = torch.full((M, nh, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    err = _err()
-    ops.gemm_tc_qkv(x, w, bias, q, positions, tok_seg, table, rd, kc, vc, bt, pages, 1 << 20, nkv, ksplit, err)
-    total = x.float() @ w.float().T + bias.float()
-    tq = total[:, :nh * hd].view(M, nh, hd)
-    tk = total[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd)
-    tv = total[:, (nh + nkv) * hd:].view(M, nkv, hd)
-    rq = ref_rope(tq, positions, inv, rd) if rd else tq
-    rk = ref_rope(tk, positions, inv, rd) if rd else tk
-    scale = float(total.abs().max())
-    tol = dict(atol=1e-2 * scale, rtol=2e-2)
-    assert int(err) == 0 and torch.allclose(q.float(), rq, **tol)
-    for t in range(M):
-        p_ = int(positions[t])
-        page = int(bt[t, p_ // P])
-        assert torch.allclose(kc[page, p_ % P].float(), rk[t], **tol)
-        assert torch.allclose(vc[page, p_ % P].float(), tv[t], **tol)
-    assert int((kc != 0).any(dim=-1).any(dim=-1).sum()) <= M
-
-
 def test_sample_greedy_and_temperature():
     ops = _ops()
     R, V = 9, 152064 // 8 + 5
@@ -497,8 +487,7 @@ DECODE_CASES = [
 
 
 @pytest.mark.parametrize("case", DECODE_CASES)
-@pytest.mark.parametrize("fused_merge", ["last_cta", "kernel", "cluster"])
-def test_attention_decode_bf16(case, fused_merge):
+def test_attention_decode_bf16(case):
     ops = _ops()
     nh, nkv, hd, P, window, ctxs, nsplit = case
     c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=21)
@@ -508,19 +497,17 @@ def test_attention_decode_bf16(case, fused_merge):
     err = _err()
     scale = hd ** -0.5
     ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
-    for _ in range(2):                               # twice: the counters of the fused merge reset themselves
+    for _ in range(2):
         out.fill_(float("nan"))
         ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
-                                  nsplit, part_o, part_ml, err, fused_merge=fused_merge == "last_cta",
-                                  cluster=fused_merge == "cluster")
+                                  nsplit, part_o, part_ml, err)
         assert int(err) == 0 and not torch.isnan(out.float()).any()
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
 @pytest.mark.parametrize("case", DECODE_CASES + [(8, 2, 64, 16, 40, [100, 39, 40, 41, 0], 3)])
-@pytest.mark.parametrize("merge", ["last_cta", "kernel"])
 @pytest.mark.parametrize("bias_dtype", [None, torch.bfloat16, torch.float32])
-def test_attention_decode_finishes_the_qkv_projection(case, merge, bias_dtype):
+def test_attention_decode_finishes_the_qkv_projection(case, bias_dtype):
     """The decode kernel given the projection's partial sums instead of q and a filled cache: the same output
     and the same cache contents as the rotary + store kernel followed by the plain decode kernel.  The
     tokens' own cache rows hold NaN beforehand: they must be computed, not read."""
@@ -542,7 +529,7 @@ def test_attention_decode_finishes_the_qkv_projection(case, merge, bias_dtype):
     mk = lambda: (torch.full((T, nh, nsplit, hd), float("nan"), device=DEV), torch.full((T, nh, nsplit, 2), float("nan"), device=DEV))
     po, pml = mk()
     ops.attention_decode_bf16(q, want, k1, v1, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale, nsplit, po, pml,
-                              err, fused_merge=False, cluster=False)
+                              err)
     ref = ref_paged_attention(q, k1, v1, c.bt, c.positions, c.tok_seg, window, scale)
     assert int(err) == 0 and torch.allclose(want.float(), ref, atol=2e-2, rtol=2e-2)
     # one kernel
@@ -554,7 +541,7 @@ def test_attention_decode_finishes_the_qkv_projection(case, merge, bias_dtype):
         got = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
         po, pml = mk()
         ops.attention_decode_qkv_bf16(parts, bias, table, 1 << 20, got, k2, v2, c.bt, c.positions, c.tok_seg, c.num_pages,
-                                      nh, window, scale, nsplit, po, pml, err, fused_merge=merge == "last_cta")
+                                      nh, window, scale, nsplit, po, pml, err)
         assert int(err) == 0 and not torch.isnan(got.float()).any()
         assert torch.allclose(got.float(), want.float(), atol=4e-3, rtol=1e-2), float((got.float() - want.float()).abs().max())
     # the caches agree wherever a request owns the slot (both hold NaN elsewhere)
