@@ -61,7 +61,13 @@ class ModelRunner:
         self.storage = CacheStorage(self.groups, self.where, page_size, pages, max_seqs, self.device, dtype)
         self.pad_page = {g: pages[g] for g in self.paged_groups}      # each group's scratch page
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.use_cuda_graph = bool(use_cuda_graph)
+        # a mixer that needs the host's copy of the step (a state mixer, unless it says otherwise) keeps
+        # the whole model out of graphs: such steps run eagerly, with the same results
+        from ..parts.base import Mixer
+        self.graph_safe = all(
+            (m.graph_safe if m.graph_safe is not None else m.cache_need().kind != "state")
+            for m in model.walk() if isinstance(m, Mixer))
+        self.use_cuda_graph = bool(use_cuda_graph) and self.graph_safe
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]
         self._graphs: Dict[int, dict] = {}
         self.graph_kernel_launches = 0       # kernels of this library replayed inside graphs

@@ -7,10 +7,18 @@ are parameters."""
 
 from __future__ import annotations
 
+import warnings
 from typing import Optional
 
+import torch
+
+from ..config.model_config import ConfigError
 from .base import CacheNeed, Mixer, ParamSpec, PartSpec, WeightSource, build_part, register_part
 from .. import ops
+
+
+_warned = set()
+MAX_HEAD_DIM = 256        # the shape-generic attention kernel keeps one head's row in a warp's registers
 
 
 @register_part("mixer", "gqa_attention")
@@ -19,7 +27,10 @@ class GQAAttention(Mixer):
                  qkv_bias: bool = True, o_bias: bool = False, window: Optional[int] = None,
                  position: Optional[PartSpec] = None, scale: Optional[float] = None):
         if num_heads % num_kv_heads:
-            raise ValueError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
+            raise ConfigError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
+        if not 2 <= int(head_dim) <= MAX_HEAD_DIM or int(head_dim) % 2:
+            raise ConfigError(f"head_dim {head_dim}: the attention kernels take even head sizes from 2 to "
+                              f"{MAX_HEAD_DIM}")
         self.hidden_size, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.qkv_bias, self.o_bias = bool(qkv_bias), bool(o_bias)
         self.window = None if window is None else int(window)
@@ -50,6 +61,19 @@ class GQAAttention(Mixer):
         if self.o_bias:
             ps.append(ParamSpec("o_b", (WeightSource("o_proj.bias", (H,), "bias"),)))
         return ps
+
+    def on_bound(self):
+        # Said once, when the model is built, not found out from the step time: in bfloat16 the tensor-core
+        # attention kernels take head sizes 64 and 128 with up to 16 query heads per kv head; every other
+        # shape runs on the shape-generic kernel (one warp per token and head), correct but far slower.
+        if self.dtype == torch.bfloat16 and not ops.attention_bf16_shape_ok(self.hd, self.nh, self.nkv):
+            key = (self.hd, self.nh, self.nkv)
+            if key not in _warned:
+                _warned.add(key)
+                warnings.warn(f"attention with head_dim {self.hd}, {self.nh} heads, {self.nkv} kv heads runs on the "
+                              f"shape-generic kernel in bfloat16 (the tensor-core kernels take head_dim 64 or 128 "
+                              f"and up to 16 query heads per kv head): correct, but much slower", RuntimeWarning,
+                              stacklevel=2)
 
     def forward(self, ctx, x, cache):
         T, qs, kvs = x.shape[0], self.q_size, self.kv_size

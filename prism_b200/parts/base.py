@@ -148,6 +148,12 @@ class Part:
     def on_bound(self) -> None:
         """Hook: create device buffers that are not weights (tables, scratch)."""
 
+    def walk(self):
+        """This part and every part below it."""
+        yield self
+        for child in self.children.values():
+            yield from child.walk()
+
 
 class Norm(Part):
     category = "norm"
@@ -174,6 +180,11 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     category = "mixer"
+    # Whether a pure-decode step with this mixer may be replayed from a captured CUDA graph.  Inside a
+    # graph there is no host copy of the step (``ctx.host`` and ``StateCacheView.host_slots`` are None)
+    # and every value must come from device arrays.  None: yes unless the mixer keeps per-request state
+    # (``cache_need().kind == "state"``); a state mixer that works from ``cache.slots`` alone sets True.
+    graph_safe: Optional[bool] = None
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed()

@@ -7,7 +7,7 @@ import pytest
 import torch
 from safetensors.torch import load_file, save_file
 
-from helpers import TINY_A, TINY_B, TINY_C, model_folder
+from helpers import TINY_A, TINY_B, TINY_C, TINY_D, model_folder
 
 from prism_b200.config.model_config import ConfigError
 from prism_b200.models.qwen2 import Qwen2Config
@@ -67,6 +67,24 @@ def test_an_architecture_is_a_module_that_registers_itself():
         assert "Qwen2" not in text and "qwen2" not in text, rel
     with pytest.raises(ConfigError, match="architectures"):
         write_model_folder({k: v for k, v in TINY_A.items() if k != "architectures"}, 0, "/nonexistent")
+
+
+def test_sizes_no_kernel_takes_are_refused_when_the_model_is_built():
+    """A head size beyond the attention kernels' limit is a configuration error at build time, not a kernel
+    error at the first step; a shape that only the slow shape-generic kernel takes in bfloat16 is said so
+    once, when the weights are bound."""
+    with pytest.raises(ConfigError, match="head_dim 258"):
+        build_model(dict(TINY_A, head_dim=258))
+    build_model(dict(TINY_A, head_dim=256))
+    import prism_b200.parts.attention as att
+    att._warned.clear()
+    with pytest.warns(RuntimeWarning, match="shape-generic kernel"):
+        load_model_folder(model_folder("A"), "cpu", torch.bfloat16)          # head_dim 16
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        load_model_folder(model_folder("A"), "cpu", torch.float32)           # float32 has one kernel: nothing to say
+        load_model_folder(model_folder("D"), "cpu", torch.bfloat16)          # head_dim 64: the tensor-core kernels
 
 
 def test_registry():

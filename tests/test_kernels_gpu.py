@@ -471,6 +471,13 @@ def test_attention_generic_rejects_big_head():
                               c.num_pages, None, 1.0, _err())
 
 
+def test_the_host_side_shape_rule_is_the_library_s():
+    ops = _ops()
+    for hd in (16, 32, 48, 64, 80, 96, 128, 256):
+        for nh, nkv in ((4, 2), (28, 4), (40, 8), (32, 1), (16, 1), (17, 1), (3, 3), (6, 4)):
+            assert ops.attention_bf16_shape_ok(hd, nh, nkv) == ops.attention_bf16_supported(hd, nh, nkv), (hd, nh, nkv)
+
+
 DECODE_CASES = [
     # nh, nkv, hd, P, window, contexts (cached lens; one new token each), nsplit
     (28, 4, 128, 256, None, [2048, 1, 0, 255, 256, 257, 4000], 10),

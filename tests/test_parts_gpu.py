@@ -277,6 +277,39 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
                     assert err < 5e-5, (rid, pos, err)
 
 
+def test_toy_state_mixer_with_cuda_graphs_requested():
+    """A mixer that keeps per-request state reads the host's copy of the step (its slots), which a
+    captured graph does not have: asked for graphs, the runner runs such a model eagerly instead of
+    capturing it - the decoded tokens' logits are those of the plain model, not a crash."""
+    from safetensors.torch import load_file
+    from prism_b200.engine.runner import ModelRunner
+    from prism_b200.weights.loader import load_model_folder
+    from prism_b200.weights.random_init import write_model_folder
+    from helpers import run_trace, trace_tail, trace_budget
+    register_toy()
+    raw = dict(architectures=["ToyDecayForCausalLM"], hidden_size=48, intermediate_size=80, vocab_size=97)
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(raw, 11, d, store_dtype=torch.float32)
+        t = load_file(d + "/model.safetensors")
+        seqs = {f"r{i}": random_tokens(97, n, 50 + i) for i, n in enumerate([19, 33])}
+        steps = trace_tail(seqs, 12)                     # the last 12 tokens one by one: pure-decode steps
+        _, model, pool = load_model_folder(d, DEV, torch.float32)
+        runner = ModelRunner(model, DEV, torch.float32, 8, trace_budget(steps, 8) // 8, 4, use_cuda_graph=True,
+                             graph_batch_sizes=(1, 2))
+        assert not runner.graph_safe and not runner.use_cuda_graph
+        got = run_trace(runner, steps)
+        assert not runner._graphs
+        for rid, seq in seqs.items():
+            ref = toy_plain(t, seq)
+            for pos in range(len(seq)):
+                assert float((got[(rid, pos)] - ref[pos]).abs().max()) < 5e-5, (rid, pos)
+    # the stock attention model keeps its graphs
+    from helpers import model_folder
+    _, m2, pool2 = load_model_folder(model_folder("A"), DEV, torch.float32)
+    r2 = ModelRunner(m2, DEV, torch.float32, 16, 8, 4, use_cuda_graph=True, graph_batch_sizes=(1, 2))
+    assert r2.graph_safe and r2.use_cuda_graph
+
+
 # --------------------------------------------------------------------------
 # a second toy architecture: a position encoding with weights of its own (a learned
 # table added to q and k) and a feed-forward with routing (top-1 of small experts,
