@@ -10,7 +10,8 @@ them (embedding, layers in order - norm, q, k, v, their biases, o, norm, gate,
 up, down - final norm, head unless tied), and are then rounded to the stored
 dtype.  For a pool each tensor is drawn on the device from a generator seeded
 with ``seed + its index`` in that same order, so large models need no host
-memory and no file.
+memory and no file; a folder written with ``device="cuda"`` draws the same way
+and so holds exactly the tensors of the pool with that seed (in bfloat16).
 """
 
 from __future__ import annotations
@@ -42,14 +43,24 @@ def _draw(shape, init: str, gen: torch.Generator, device="cpu") -> torch.Tensor:
 
 
 def write_model_folder(raw_config: dict, seed: int, out_dir: str,
-                       store_dtype: torch.dtype = torch.bfloat16) -> str:
-    """Write ``config.json`` and ``model.safetensors`` for ``raw_config``."""
+                       store_dtype: torch.dtype = torch.bfloat16, device="cpu") -> str:
+    """Write ``config.json`` and ``model.safetensors`` for ``raw_config``.  ``device``: where the values
+    are drawn.  ``"cpu"``: one generator, tensor after tensor.  A CUDA device (for models of billions of
+    parameters, where the host's generator takes minutes): every tensor from a generator of its own,
+    seeded ``seed + index``, as ``random_pool`` draws them."""
     from safetensors.torch import save_file
     raw = dict(raw_config)           # must name its architecture, as a config.json does
     _, model = build_model(raw)
-    gen = torch.Generator().manual_seed(int(seed))
-    tensors = {name: _draw(shape, init, gen).to(store_dtype).contiguous()
-               for name, shape, init in file_tensors(model)}
+    if torch.device(device).type == "cpu":
+        gen = torch.Generator().manual_seed(int(seed))
+        tensors = {name: _draw(shape, init, gen).to(store_dtype).contiguous()
+                   for name, shape, init in file_tensors(model)}
+    else:
+        tensors = {}
+        for idx, (name, shape, init) in enumerate(file_tensors(model)):
+            gen = torch.Generator(device=device).manual_seed(int(seed) + idx)
+            t = torch.empty(shape, dtype=store_dtype, device=device).normal_(0.0, STD, generator=gen)
+            tensors[name] = (t.add_(1.0) if init == "norm" else t).cpu()
     os.makedirs(out_dir, exist_ok=True)
     raw["torch_dtype"] = {torch.bfloat16: "bfloat16", torch.float32: "float32"}.get(store_dtype, str(store_dtype))
     with open(os.path.join(out_dir, "config.json"), "w") as f:

@@ -4,8 +4,9 @@ This file is the oracle of the test-suite.  It is written from the formulas
 of andre-fu/prism's executor (cited per function as ``file:line`` inside that
 project) and shares no code with the ``prism_b200`` package: it reads
 ``config.json`` with ``json`` and ``model.safetensors`` with the safetensors
-library, keeps every tensor in float32 on the CPU, has no cache, no paging
-and no batching.  One function per part.
+library, keeps every tensor in float32 (on the CPU, or on the device the
+folder is loaded to: every function works where its tensors are), has no
+cache, no paging and no batching.  One function per part.
 
 Where the executor computes in reduced precision (bf16 RoPE tables, bf16
 stores) this file computes in float32: it states the mathematics, and the
@@ -30,13 +31,13 @@ from safetensors.torch import load_file
 # model folder
 # --------------------------------------------------------------------------
 
-def load_folder(model_dir: str):
+def load_folder(model_dir: str, device="cpu"):
     """Read ``config.json`` and every tensor of ``model.safetensors`` (as
-    float32).  Tied heads: ``lm_head.weight`` is the embedding matrix
-    (engine/weight_manager.py:84-86, engine/weight_pool.py:157-160)."""
+    float32, onto ``device``).  Tied heads: ``lm_head.weight`` is the embedding
+    matrix (engine/weight_manager.py:84-86, engine/weight_pool.py:157-160)."""
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
-    tensors = {k: v.to(torch.float32) for k, v in
+    tensors = {k: v.to(device=device, dtype=torch.float32) for k, v in
                load_file(os.path.join(model_dir, "model.safetensors")).items()}
     if "lm_head.weight" not in tensors:
         tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"]
@@ -87,7 +88,7 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 def rope_angles(positions: torch.Tensor, head_dim: int, theta: float) -> torch.Tensor:
     """``freqs = pos (x) theta^(-2j/hd)`` (engine/executor.py:48-52), float32."""
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
-    return torch.outer(positions.to(torch.float32), inv_freq)      # [T, hd/2]
+    return torch.outer(positions.to(torch.float32), inv_freq.to(positions.device))      # [T, hd/2]
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:
@@ -121,7 +122,7 @@ def attention(q, k, v, window=None) -> torch.Tensor:
     nkv = k.shape[1]
     g = nh // nkv
     out = torch.empty_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     mask = pos[None, :] <= pos[:, None]
     if window is not None:
         mask &= pos[None, :] > pos[:, None] - window
@@ -169,8 +170,9 @@ def forward(cfg: dict, t: dict, tokens, cos_sin=None) -> torch.Tensor:
     """Logits at every position of one whole sequence, float32 [T, V]
     (engine/executor.py:99-130, with the head applied to all rows).
     ``cos_sin``: rotary tables to use instead of the float32 ones."""
-    tokens = torch.as_tensor(tokens, dtype=torch.long)
-    positions = torch.arange(tokens.shape[0])
+    dev = t["model.embed_tokens.weight"].device
+    tokens = torch.as_tensor(tokens, dtype=torch.long, device=dev)
+    positions = torch.arange(tokens.shape[0], device=dev)
     x = embed(tokens, t["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, t, i, cfg, positions, cos_sin)

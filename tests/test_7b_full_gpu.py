@@ -1,0 +1,156 @@
+"""The whole Qwen2.5-7B shape - 28 layers, hidden 3584, 28/4 heads of 128,
+intermediate 18944, vocabulary 152064, untied head, pages of 256 tokens - with
+random weights, against the plain model (GPU).
+
+What the tiny configurations and the two-layer files cannot show: the error
+that 28 layers of bfloat16 accumulate, the head product over the full
+vocabulary (1,188 weight tiles), and the float32 path at the size it is meant
+to be checked at.  The plain model (``tests/plain/qwen2_plain.py``, whole
+sequences, no cache, shares no code with the engine) runs here on the GPU in
+float32 with TF32 switched off; the engine is compared with it in float32 and
+in bfloat16, in the four ways of cutting the work: every request alone and
+whole; all but the last 32 tokens in one step, then token by token; in
+portions of changing size; and mixed, up to four requests live, portions of
+some beside decoded tokens of others, with exactly as many pages as the trace
+needs, so that pages are used again while they hold another request's keys.
+
+Tolerances.  float32: 1e-3 absolute on every logit (the logits' scale is about
+one; measured errors are a few 1e-5).  bfloat16: every logit within 3 % of the
+sequence's largest logit magnitude, and the two orderings agree where it
+counts - the plain model's best token is among the engine's five best at
+every position (with random weights the best logits lie closer together than
+trained ones do, so the first place itself may swap).
+"""
+
+import os
+import tempfile
+
+import pytest
+import torch
+
+from helpers import P, random_tokens, run_trace, trace_budget, trace_mixed, trace_portions, trace_tail, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+PAGE = 256
+QWEN25_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=28, hidden_size=3584,
+                 num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+                 vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                 max_position_embeddings=32768, use_sliding_window=False)
+# five requests for four places: the fifth takes over pages that the first to finish gives back
+LENGTHS = {"a": 300, "b": 77, "c": 150, "d": 41, "e": 260}
+
+
+@pytest.fixture(scope="module")
+def full_model():
+    """The model folder (written once, values drawn on the GPU), the sequences, and the plain model's
+    logits for each whole sequence, computed on the GPU in true float32."""
+    from prism_b200.weights.random_init import write_model_folder
+    tf32 = (torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    with tempfile.TemporaryDirectory(prefix="prism_7b_full_") as d:
+        write_model_folder(QWEN25_7B, 17, d, device=DEV)
+        seqs = {rid: random_tokens(QWEN25_7B["vocab_size"], n, 100 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+        cfg, t = P.load_folder(d, device=DEV)
+        with torch.no_grad():
+            ref = {rid: P.forward(cfg, t, seq).cpu() for rid, seq in seqs.items()}
+        del t
+        torch.cuda.empty_cache()
+        yield d, seqs, ref
+    torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = tf32
+
+
+_runners = {}
+
+
+def engine_for(folder, dtype):
+    """Model and weights once per dtype (30 GB in float32); every trace gets a runner, and so a cache, of its own."""
+    from prism_b200.weights.loader import load_model_folder
+    if dtype not in _runners:
+        _runners.clear()
+        torch.cuda.empty_cache()
+        _runners[dtype] = load_model_folder(folder, DEV, getattr(torch, dtype))
+    return _runners[dtype]
+
+
+TRACES = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 32), "portions": trace_portions,
+          "mixed": lambda s: trace_mixed(s, seed=11)}
+
+
+@pytest.mark.parametrize("mode", list(TRACES))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_size_logits(full_model, dtype, mode):
+    from prism_b200.engine.runner import ModelRunner
+    folder, seqs, ref = full_model
+    _, model, pool = engine_for(folder, dtype)
+    steps = TRACES[mode](seqs)
+    runner = ModelRunner(model, DEV, getattr(torch, dtype), PAGE, trace_budget(steps, PAGE) // PAGE, 4, max_seq_len=512,
+                         use_cuda_graph=(dtype == "bfloat16"), graph_batch_sizes=(1, 2, 4))
+    got = run_trace(runner, steps)
+    assert runner.cache.pages_in_use() == 0
+    worst_abs, worst_rel, top1_same, top1_in_top5, n = 0.0, 0.0, 0, 0, 0
+    for rid, seq in seqs.items():
+        scale = float(ref[rid].abs().max())
+        for pos in range(len(seq)):
+            g, r = got[(rid, pos)], ref[rid][pos]
+            err = float((g - r).abs().max())
+            worst_abs, worst_rel = max(worst_abs, err), max(worst_rel, err / scale)
+            best = int(r.argmax())
+            top1_same += int(g.argmax()) == best
+            top1_in_top5 += best in g.topk(5).indices.tolist()
+            n += 1
+            if dtype == "float32":
+                assert err <= 1e-3, (rid, pos, err, scale)
+            else:
+                assert err <= 3e-2 * scale, (rid, pos, err, scale)
+                assert best in g.topk(5).indices.tolist(), (rid, pos, "the plain model's best token is not among the engine's five best")
+    print(f"\n7B full size, {dtype}, {mode}: {n} positions, worst abs error {worst_abs:.3e}, worst relative to the "
+          f"logit scale {worst_rel:.3e}, same best token at {top1_same}/{n}, best token in the engine's top five at {top1_in_top5}/{n}")
+
+
+@pytest.mark.parametrize("M", [1, 8, 64])
+def test_head_product_over_the_full_vocabulary(M):
+    """``logits = h @ lm_head^T`` at N = 152,064 (executor.py:130) on the path the engine takes for M rows -
+    the tcgen05 weight-streaming kernel with float32 output up to 16 rows, the library product above -
+    against a float32 matmul with TF32 off."""
+    from prism_b200 import ops
+    V, H = 152064, 3584
+    g = torch.Generator(device=DEV).manual_seed(3)
+    w = torch.empty(V, H, dtype=torch.bfloat16, device=DEV).normal_(0.0, 0.02, generator=g)
+    x = torch.empty(M, H, dtype=torch.bfloat16, device=DEV).normal_(0.0, 1.0, generator=g)
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = x.float() @ w.float().T
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+    out = ops.linear(x, w, None, out_dtype=torch.float32)
+    ops.check_tc_errors()
+    assert out.dtype == torch.float32 and out.shape == (M, V)
+    scale = float(ref.abs().max())
+    err = float((out - ref).abs().max())
+    assert err <= 1e-3 * scale, (M, err, scale)             # bf16 inputs, float32 accumulation: only the order of additions differs
+    # the last tile is a partial one (152,064 = 1,188 * 128 exactly) and the first rows of every tile are checked above;
+    # a vocabulary that is no multiple of 128 as well:
+    V2 = 151_937
+    out2 = ops.linear(x, w[:V2], None, out_dtype=torch.float32)
+    assert float((out2 - ref[:, :V2]).abs().max()) <= 1e-3 * scale
+
+
+def test_folder_written_on_the_gpu_holds_the_pool_s_tensors():
+    """``write_model_folder(..., device=cuda)`` and ``random_pool`` with the same seed are the same model."""
+    from safetensors.torch import load_file
+    from prism_b200.model_registry import build_model
+    from prism_b200.weights.random_init import random_pool, write_model_folder
+    from helpers import TINY_B
+    with tempfile.TemporaryDirectory() as d:
+        write_model_folder(TINY_B, 5, d, device=DEV)
+        t = load_file(os.path.join(d, "model.safetensors"))
+    _, model = build_model(TINY_B)
+    pool = random_pool(model, 5, DEV, torch.bfloat16)
+    q = torch.cat([t[f"model.layers.1.self_attn.{n}_proj.weight"] for n in "qkv"])
+    assert torch.equal(pool["layers.1.mixer.qkv_w"].cpu(), q)
+    assert torch.equal(pool["final_norm.weight"].cpu(), t["model.norm.weight"])
+    assert torch.equal(pool["head.weight"].cpu(), t["lm_head.weight"])

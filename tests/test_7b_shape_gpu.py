@@ -41,12 +41,12 @@ def folder_and_plain(request):
         yield d, seqs, ref
 
 
-def runner_for(folder, dtype, num_pages, page_size=64, graphs=False):
+def runner_for(folder, dtype, num_pages, page_size=64, graphs=False, max_seqs=8):
     from prism_b200.engine.runner import ModelRunner
     from prism_b200.weights.loader import load_model_folder
     tdt = getattr(torch, dtype)
     _, model, pool = load_model_folder(folder, "cuda:0", tdt)
-    r = ModelRunner(model, "cuda:0", tdt, page_size, num_pages, 8, max_seq_len=512, use_cuda_graph=graphs,
+    r = ModelRunner(model, "cuda:0", tdt, page_size, num_pages, max_seqs, max_seq_len=512, use_cuda_graph=graphs,
                     graph_batch_sizes=(1, 4))
     r._pool = pool
     return r
@@ -121,6 +121,69 @@ def test_7b_sized_layers_with_the_projection_finished_inside_decode_attention(fo
             err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
             assert err <= 5e-3 + 4e-2 * scale, (rid, pos, err, scale)
     assert runner.cache.pages_in_use() == 0
+
+
+def test_thirteen_decoding_requests_beside_a_prompt_portion(folder_and_plain, monkeypatch):
+    """A mixed step as the scheduler builds it under load: thirteen requests each feed one decoded token
+    and a fourteenth a portion of its prompt.  From twelve single tokens at the head of the batch on
+    (``ops.MIXED_SPLIT_MIN``, at its default here) those go to the decode attention kernel and only the
+    portion to the prefill kernel - in one step, over one block table.  Every logit row against the plain model."""
+    from prism_b200 import ops
+    folder, _, _ = folder_and_plain
+    assert ops.MIXED_SPLIT_MIN == 12
+    calls = []
+    real = ops.attention_decode_bf16
+    monkeypatch.setattr(ops, "attention_decode_bf16", lambda q, *a, **k: (calls.append(q.shape[0]), real(q, *a, **k))[1])
+    cfg, t = P.load_folder(folder, device="cuda:0")
+    seqs = {f"d{i}": random_tokens(8192, 21 + 3 * i, 400 + i) for i in range(13)}
+    seqs["long"] = random_tokens(8192, 230, 77)
+    with torch.no_grad():
+        ref = {k: P.forward(cfg, t, v).cpu() for k, v in seqs.items()}
+    steps, n = [], 0
+    for rid in list(seqs)[:13]:                          # the short ones whole but for their last six tokens
+        head = len(seqs[rid]) - 6
+        steps.append(dict(step=n, entries=[dict(id=rid, tokens=seqs[rid][:head], want=list(range(head)))], end=[]))
+        n += 1
+    at = 0
+    for j in range(6):                                   # six steps: thirteen single tokens + a portion of the long prompt
+        entries = [dict(id=rid, tokens=[seqs[rid][len(seqs[rid]) - 6 + j]], want=[0]) for rid in list(seqs)[:13]]
+        m = (70, 2, 64, 33, 60, 1)[j]
+        entries.append(dict(id="long", tokens=seqs["long"][at:at + m], want=list(range(m))))
+        at += m
+        steps.append(dict(step=n, entries=entries, end=list(seqs) if j == 5 else []))
+        n += 1
+    assert at == 230
+    runner = runner_for(folder, "bfloat16", trace_budget(steps, 64) // 64, max_seqs=14)
+    got = run_trace(runner, steps)
+    assert calls.count(13) >= 6 * 2, calls               # every mixed step, every layer: thirteen tokens on the decode kernel
+    for rid, seq in seqs.items():
+        scale = float(ref[rid].abs().max())
+        for pos in range(len(seq)):
+            err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
+            assert err <= 5e-3 + 4e-2 * scale, (rid, pos, err, scale)
+
+
+def test_generation_with_prompts_prefilled_in_portions(folder_and_plain):
+    """``Engine.generate`` with ``prefill_chunk`` shorter than the prompts and a token budget that makes
+    portions share steps with decoding requests, at these layer sizes, CUDA graphs and pipelined decoding on:
+    every generated token is the plain model's best one for the same history (up to a near-tie)."""
+    from prism_b200 import Engine, EngineConfig, SamplingParams, SchedulerConfig
+    folder, _, _ = folder_and_plain
+    cfg, t = P.load_folder(folder, device="cuda:0")
+    ec = EngineConfig(kv_page_size=64, num_pages=24, max_seq_len=512, use_cuda_graph=True, graph_batch_sizes=(1, 2, 4),
+                      scheduler=SchedulerConfig(max_batch_tokens=96, max_num_seqs=4, prefill_chunk=80))
+    eng = Engine(folder, ec, dtype="bfloat16")
+    prompts = [random_tokens(8192, n, 500 + n) for n in (200, 33, 150, 7, 90)]
+    res = eng.generate(prompts, [SamplingParams(max_new_tokens=n) for n in (6, 14, 9, 20, 5)])
+    assert eng.stats.prefill_tokens >= sum(len(p) for p in prompts) and eng.runner.graph_kernel_launches > 0
+    assert eng.cache.pages_in_use() == 0
+    with torch.no_grad():
+        for p, r in zip(prompts, res):
+            assert r.finish_reason == "length"
+            lg = P.forward(cfg, t, list(p) + list(r.token_ids))            # one pass: row i predicts token i + 1
+            for i, tok in enumerate(r.token_ids):
+                row = lg[len(p) - 1 + i]
+                assert float(row.max() - row[tok]) <= 0.03 * float(row.abs().max()), (len(p), i, tok)
 
 
 def test_a_step_gives_the_same_bits_every_time():

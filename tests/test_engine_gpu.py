@@ -94,6 +94,35 @@ def test_preemption_recomputes_and_keeps_the_tokens():
     assert got[0].token_ids == P.generate(cfg, t, prompts[0], 24)
 
 
+def test_preemption_under_pipelined_decoding_with_graphs_in_bfloat16():
+    """Everything on at once, on the tensor-core kernels (config D: heads of 64): decode graphs, pipelined
+    decoding (a step launched before the last one's tokens are read) and a pool too small for the running
+    requests, so that requests are preempted while a step may be in flight and recomputed later from
+    pages that others have used.  The tokens are those of an ample pool, and the plain model's."""
+    from prism_b200 import SamplingParams
+    vocab = TINY["D"][0]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 600 + n) for n in (70, 45, 100, 20)]
+    sp = SamplingParams(max_new_tokens=60)
+    kw = dict(graph=True, page_size=32, max_num_seqs=4, prefill_chunk=64, max_batch_tokens=128)
+    ample_eng = engine("D", "bfloat16", num_pages=64, **kw)
+    ample = ample_eng.generate(prompts, sp)
+    assert ample_eng.stats.preemptions == 0
+    tight_eng = engine("D", "bfloat16", num_pages=12, **kw)           # 384 tokens of cache for 130 + 105 + 160 + 80
+    assert tight_eng.scheduler.config.async_decode
+    got = tight_eng.generate(prompts, sp)
+    assert tight_eng.stats.preemptions > 0 and tight_eng.runner.graph_kernel_launches > 0
+    assert tight_eng.cache.pages_in_use() == 0
+    for p, a, b in zip(prompts, ample, got):
+        assert len(b.token_ids) == 60
+        near_greedy("D", p, b.token_ids, 0.03)
+        if a.token_ids != b.token_ids:
+            # recomputing a request cuts its work differently, which changes bfloat16 rounding: the two runs may
+            # part ways, but only where the plain model itself sees a near-tie between the two tokens
+            i = next(j for j, (x, y) in enumerate(zip(a.token_ids, b.token_ids)) if x != y)
+            lg = plain_logits("D", list(p) + list(b.token_ids[:i]))[-1]
+            assert abs(float(lg[a.token_ids[i]] - lg[b.token_ids[i]])) <= 0.03 * float(lg.abs().max()), (i, a.token_ids[i], b.token_ids[i])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(dtype):
     """One token a step from the first position on, for 300 steps across many
