@@ -17,7 +17,7 @@ import torch
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from bench import QWEN25_7B  # noqa: E402
+from bench import BASE, SHAPES  # noqa: E402
 from prism_b200 import Engine, EngineConfig, SchedulerConfig, ops  # noqa: E402
 from prism_b200.engine.batch import Segment  # noqa: E402
 
@@ -30,10 +30,8 @@ def main():
     ap.add_argument("--shape", default="7b", choices=["7b", "14b", "32b"], help="layer sizes (Qwen2.5-7B / 14B / 32B)")
     args = ap.parse_args()
     B = args.batch
-    cfg = dict(QWEN25_7B, num_hidden_layers=args.layers)
-    if args.shape != "7b":
-        from workloads import SHAPES
-        cfg.update(SHAPES[args.shape], num_hidden_layers=args.layers)
+    cfg = dict(BASE, **SHAPES[args.shape])
+    cfg["num_hidden_layers"] = args.layers
     pages = (args.context + 256) // 256 + 1
     ec = EngineConfig(kv_page_size=256, num_pages=B * pages + 8, max_seq_len=4096, use_cuda_graph=True,
                       graph_batch_sizes=(B,), scheduler=SchedulerConfig(max_num_seqs=B))

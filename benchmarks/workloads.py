@@ -21,17 +21,12 @@ import torch
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
 from prism_b200 import Engine, EngineConfig, SamplingParams, SchedulerConfig  # noqa: E402
 
-BASE = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", head_dim=128, vocab_size=152064, rope_theta=1000000.0,
-            rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False)
-SHAPES = {
-    "14b": dict(num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=13824),
-    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=27648),
-}
+from bench import BASE, SHAPES  # noqa: E402
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=sorted(SHAPES))
+    ap.add_argument("which", choices=["14b", "32b"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in the output)")
     args = ap.parse_args()
     cfg = dict(BASE, **SHAPES[args.which])
