@@ -81,6 +81,7 @@ PRISM_EXPORT int prism_attention_merge_bf16(const float* part_o, const float* pa
                                             int out_stride, int T, int nh, int hd, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (nsplit < 1 || (hd != 64 && hd != 128)) return (int)cudaErrorInvalidValue;
+    // one thread per output element: the block size is the head size
     if (hd == 64)
         return (int)prism::launch_kernel(prism::attn_merge_kernel<64>, dim3(T * nh), dim3(64), 0, stream, part_o, part_ml,
                                          nsplit, (__nv_bfloat16*)out, out_stride, nh);

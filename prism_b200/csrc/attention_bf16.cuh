@@ -385,25 +385,79 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 }
 
 // merge the splits: out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
+// One CTA per (token, head), one thread per output element.  The kernel is all latency (a few KB per CTA), so
+// it makes as few dependent trips to memory as it can: every thread asks for its first MERGE_BATCH partial
+// outputs at once, before anything is known about their weights; meanwhile the first warp fetches all
+// (max, sum) pairs in one round, reduces them with shuffles and leaves one weight per split in shared memory.
+constexpr int MERGE_BATCH = 16;
+constexpr int MERGE_MAX_SPLITS = 256;      // weights kept in shared memory; more splits than this take the slow loop
+
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   int nsplit, __nv_bfloat16* __restrict__ out, int out_stride, int nh) {
+    __shared__ float s_w[MERGE_MAX_SPLITS];
+    __shared__ float s_inv;
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
     const float* po = pdl_fresh(part_o) + (size_t)blockIdx.x * nsplit * HD;       // the attention kernel's output
     const float* pml = pdl_fresh(part_ml) + (size_t)blockIdx.x * nsplit * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
-    const float Mu = M == -INFINITY ? 0.f : M;
-    float L = 0.f;
-    for (int s = 0; s < nsplit; ++s) L += pml[2 * s + 1] * exp2_guard(pml[2 * s], Mu);
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < nsplit; ++s) acc += po[(size_t)s * HD + d] * exp2_guard(pml[2 * s], Mu);
-        out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(acc * inv);
+    const int d = threadIdx.x;                                                    // blockDim.x == HD
+    if (nsplit > MERGE_MAX_SPLITS) {
+        float M = -INFINITY;
+        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float L = 0.f, acc = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float f = exp2_guard(pml[2 * s], Mu);
+            L += pml[2 * s + 1] * f;
+            acc += po[(size_t)s * HD + d] * f;
+        }
+        out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        return;
     }
+    float v[MERGE_BATCH];
+#pragma unroll
+    for (int i = 0; i < MERGE_BATCH; ++i) v[i] = i < nsplit ? po[(size_t)i * HD + d] : 0.f;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float2* ml = reinterpret_cast<const float2*>(pml);
+        float2 mine[MERGE_MAX_SPLITS / 32];
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+            const int s = lane + 32 * i;
+            mine[i] = s < nsplit ? ml[s] : make_float2(-INFINITY, 0.f);
+            M = fmaxf(M, mine[i].x);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float Mu = M == -INFINITY ? 0.f : M;
+        float L = 0.f;
+#pragma unroll
+        for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+            const int s = lane + 32 * i;
+            const float f = exp2_guard(mine[i].x, Mu);
+            if (s < nsplit) s_w[s] = f;
+            L += mine[i].y * f;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        if (lane == 0) s_inv = L > 0.f ? 1.f / L : 0.f;
+    }
+    __syncthreads();
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < MERGE_BATCH; ++i)
+        if (i < nsplit) acc += v[i] * s_w[i];
+    for (int s0 = MERGE_BATCH; s0 < nsplit; s0 += MERGE_BATCH) {
+#pragma unroll
+        for (int i = 0; i < MERGE_BATCH; ++i) v[i] = s0 + i < nsplit ? po[(size_t)(s0 + i) * HD + d] : 0.f;
+#pragma unroll
+        for (int i = 0; i < MERGE_BATCH; ++i)
+            if (s0 + i < nsplit) acc += v[i] * s_w[s0 + i];
+    }
+    out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(acc * s_inv);
 }
 
 // ---------------------------------------------------------------------------
@@ -609,7 +663,7 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                                    scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, err,
                                    fused != nullptr ? *fused : DecodeQKV());
     if (rc != cudaSuccess || nsplit == 1) return (int)rc;
-    return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD >= 128 ? 128 : 64), 0, stream,
+    return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD), 0, stream,
                               (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);
 }
 

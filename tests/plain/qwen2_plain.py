@@ -138,15 +138,20 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return gate * torch.sigmoid(gate) * up
 
 
-def decoder_layer(x, t, i, cfg, positions, cos_sin=None):
+def decoder_layer(x, t, i, cfg, positions, cos_sin=None, store=None):
     """One pre-norm block (engine/executor.py:106-127): norm, fused qkv with
     bias, rope on q and k, attention, o-projection + residual, norm, gate/up,
-    SwiGLU, down-projection + residual."""
+    SwiGLU, down-projection + residual.  ``store`` (default: nothing) is applied
+    wherever the executor stores an activation in its compute dtype - norm
+    output, q/k/v, rotated q and k, attention output, SwiGLU output - so that
+    ``store=lambda v: v.bfloat16().float()`` shows what that rounding alone does
+    to the result (the residual stream and all arithmetic stay float32)."""
+    store = store or (lambda v: v)
     nh, nkv, hd = sizes(cfg)
     eps = cfg.get("rms_norm_eps", 1e-6)
     p = f"model.layers.{i}."
     T = x.shape[0]
-    h = rms_norm(x, t[p + "input_layernorm.weight"], eps)
+    h = store(rms_norm(x, t[p + "input_layernorm.weight"], eps))
     q = h @ t[p + "self_attn.q_proj.weight"].T
     k = h @ t[p + "self_attn.k_proj.weight"].T
     v = h @ t[p + "self_attn.v_proj.weight"].T
@@ -155,29 +160,30 @@ def decoder_layer(x, t, i, cfg, positions, cos_sin=None):
         k = k + t[p + "self_attn.k_proj.bias"]
         v = v + t[p + "self_attn.v_proj.bias"]
     cos, sin = cos_sin if cos_sin is not None else rope_cos_sin(positions, hd, cfg.get("rope_theta", 10000.0))
-    q = apply_rope(q.view(T, nh, hd), cos, sin)
-    k = apply_rope(k.view(T, nkv, hd), cos, sin)
-    a = attention(q, k, v.view(T, nkv, hd), layer_window(cfg, i))
+    q = store(apply_rope(q.view(T, nh, hd), cos, sin))
+    k = store(apply_rope(k.view(T, nkv, hd), cos, sin))
+    a = store(attention(q, k, store(v).view(T, nkv, hd), layer_window(cfg, i)))
     x = x + a.reshape(T, nh * hd) @ t[p + "self_attn.o_proj.weight"].T
-    h = rms_norm(x, t[p + "post_attention_layernorm.weight"], eps)
+    h = store(rms_norm(x, t[p + "post_attention_layernorm.weight"], eps))
     gate = h @ t[p + "mlp.gate_proj.weight"].T
     up = h @ t[p + "mlp.up_proj.weight"].T
-    x = x + swiglu(gate, up) @ t[p + "mlp.down_proj.weight"].T
+    x = x + store(swiglu(gate, up)) @ t[p + "mlp.down_proj.weight"].T
     return x
 
 
-def forward(cfg: dict, t: dict, tokens, cos_sin=None) -> torch.Tensor:
+def forward(cfg: dict, t: dict, tokens, cos_sin=None, store=None) -> torch.Tensor:
     """Logits at every position of one whole sequence, float32 [T, V]
     (engine/executor.py:99-130, with the head applied to all rows).
-    ``cos_sin``: rotary tables to use instead of the float32 ones."""
+    ``cos_sin``: rotary tables to use instead of the float32 ones.
+    ``store``: see ``decoder_layer``."""
     dev = t["model.embed_tokens.weight"].device
     tokens = torch.as_tensor(tokens, dtype=torch.long, device=dev)
     positions = torch.arange(tokens.shape[0], device=dev)
     x = embed(tokens, t["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, t, i, cfg, positions, cos_sin)
+        x = decoder_layer(x, t, i, cfg, positions, cos_sin, store)
     h = rms_norm(x, t["model.norm.weight"], cfg.get("rms_norm_eps", 1e-6))
-    return h @ t["lm_head.weight"].T
+    return (store(h) if store else h) @ t["lm_head.weight"].T
 
 
 # --------------------------------------------------------------------------

@@ -14,12 +14,21 @@ portions of changing size; and mixed, up to four requests live, portions of
 some beside decoded tokens of others, with exactly as many pages as the trace
 needs, so that pages are used again while they hold another request's keys.
 
-Tolerances.  float32: 1e-3 absolute on every logit (the logits' scale is about
-one; measured errors are a few 1e-5).  bfloat16: every logit within 3 % of the
-sequence's largest logit magnitude, and the two orderings agree where it
-counts - the plain model's best token is among the engine's five best at
-every position (with random weights the best logits lie closer together than
-trained ones do, so the first place itself may swap).
+Tolerances.  float32: 1e-3 absolute on every logit (the logits' scale is
+about 7; measured: 1.7e-4, the same in every mode).  bfloat16 has no such
+absolute yardstick: a random-weight model of this depth amplifies a rounding
+of 2^-9 layer by layer, and what comes out is a few per cent of a row's norm
+whoever does the rounding.  So the yardstick is measured too: the plain model
+is run once more with its activations rounded to bfloat16 wherever the
+executor stores one (norm output, q/k/v, rotated q and k, attention output,
+SwiGLU output; all arithmetic and the residual stream still float32), and the
+engine's distance from the float32 logits may be at most twice the distance
+that this rounding alone produces, per request, in the row norm
+|engine - plain| / |plain| and in the largest single logit.  (Measured: the
+engine 4.6-5.1 % of the row norm, rounding alone about the same.)  And the two
+orderings agree where it counts: the plain model's best token is among the
+engine's five best at every position (with random weights the best logits lie
+closer together than trained ones do, so the first place itself may swap).
 """
 
 import os
@@ -56,9 +65,16 @@ def full_model():
         cfg, t = P.load_folder(d, device=DEV)
         with torch.no_grad():
             ref = {rid: P.forward(cfg, t, seq).cpu() for rid, seq in seqs.items()}
+            # what rounding to bfloat16 alone does to these logits: (worst row error, worst single logit) per request
+            rounding = {}
+            for rid, seq in seqs.items():
+                r16 = P.forward(cfg, t, seq, store=lambda v: v.bfloat16().float()).cpu()
+                diff = r16 - ref[rid]
+                rounding[rid] = (float((diff.norm(dim=-1) / ref[rid].norm(dim=-1)).max()), float(diff.abs().max()))
         del t
         torch.cuda.empty_cache()
-        yield d, seqs, ref
+        yield d, seqs, ref, rounding
+        _runners.clear()
     torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = tf32
 
 
@@ -75,6 +91,7 @@ def engine_for(folder, dtype):
     return _runners[dtype]
 
 
+BF16_SLACK = 2.0          # the engine's bfloat16 error may be this many times what rounding alone does to the plain model
 TRACES = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 32), "portions": trace_portions,
           "mixed": lambda s: trace_mixed(s, seed=11)}
 
@@ -83,31 +100,35 @@ TRACES = {"whole": trace_whole, "tail": lambda s: trace_tail(s, 32), "portions":
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_full_size_logits(full_model, dtype, mode):
     from prism_b200.engine.runner import ModelRunner
-    folder, seqs, ref = full_model
+    folder, seqs, ref, rounding = full_model
     _, model, pool = engine_for(folder, dtype)
     steps = TRACES[mode](seqs)
     runner = ModelRunner(model, DEV, getattr(torch, dtype), PAGE, trace_budget(steps, PAGE) // PAGE, 4, max_seq_len=512,
                          use_cuda_graph=(dtype == "bfloat16"), graph_batch_sizes=(1, 2, 4))
     got = run_trace(runner, steps)
     assert runner.cache.pages_in_use() == 0
-    worst_abs, worst_rel, top1_same, top1_in_top5, n = 0.0, 0.0, 0, 0, 0
+    worst_abs, worst_l2, top1_same, top1_in_top5, n = 0.0, 0.0, 0, 0, 0
     for rid, seq in seqs.items():
-        scale = float(ref[rid].abs().max())
+        row_bound, abs_bound = (BF16_SLACK * v for v in rounding[rid])
         for pos in range(len(seq)):
             g, r = got[(rid, pos)], ref[rid][pos]
             err = float((g - r).abs().max())
-            worst_abs, worst_rel = max(worst_abs, err), max(worst_rel, err / scale)
+            l2 = float((g - r).norm() / r.norm())
+            worst_abs, worst_l2 = max(worst_abs, err), max(worst_l2, l2)
             best = int(r.argmax())
             top1_same += int(g.argmax()) == best
             top1_in_top5 += best in g.topk(5).indices.tolist()
             n += 1
             if dtype == "float32":
-                assert err <= 1e-3, (rid, pos, err, scale)
+                assert err <= 1e-3, (rid, pos, err)
             else:
-                assert err <= 3e-2 * scale, (rid, pos, err, scale)
+                assert l2 <= row_bound, (rid, pos, l2, "rounding alone:", rounding[rid][0])
+                assert err <= abs_bound, (rid, pos, err, "rounding alone:", rounding[rid][1])
                 assert best in g.topk(5).indices.tolist(), (rid, pos, "the plain model's best token is not among the engine's five best")
-    print(f"\n7B full size, {dtype}, {mode}: {n} positions, worst abs error {worst_abs:.3e}, worst relative to the "
-          f"logit scale {worst_rel:.3e}, same best token at {top1_same}/{n}, best token in the engine's top five at {top1_in_top5}/{n}")
+    print(f"\n7B full size, {dtype}, {mode}: {n} positions, worst abs error {worst_abs:.3e}, worst row error "
+          f"|g - r| / |r| {worst_l2:.3e} (rounding alone, per request (row, abs): "
+          f"{ {k: (round(a, 4), round(b, 3)) for k, (a, b) in rounding.items()} }), same best token at {top1_same}/{n}, "
+          f"best token in the engine's top five at {top1_in_top5}/{n}")
 
 
 @pytest.mark.parametrize("M", [1, 8, 64])

@@ -147,7 +147,7 @@ def test_thirteen_decoding_requests_beside_a_prompt_portion(folder_and_plain, mo
     at = 0
     for j in range(6):                                   # six steps: thirteen single tokens + a portion of the long prompt
         entries = [dict(id=rid, tokens=[seqs[rid][len(seqs[rid]) - 6 + j]], want=[0]) for rid in list(seqs)[:13]]
-        m = (70, 2, 64, 33, 60, 1)[j]
+        m = (70, 2, 64, 33, 59, 2)[j]
         entries.append(dict(id="long", tokens=seqs["long"][at:at + m], want=list(range(m))))
         at += m
         steps.append(dict(step=n, entries=entries, end=list(seqs) if j == 5 else []))
