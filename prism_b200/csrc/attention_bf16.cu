@@ -1,10 +1,26 @@
 // extern "C" launchers of the bf16 tensor-core attention kernels (attention_bf16.cuh).
 #include "attention_bf16.cuh"
 
-// 1 if the tensor-core kernels take this shape (else the generic kernel must be used)
+// 1 if the tensor-core kernels take this shape (else the generic kernel must be used): head sizes in steps
+// of 16 up to 128 (the output row of a head stays in registers), up to 16 query heads per kv head (the rows of
+// one 16-row MMA tile in the decode kernel)
 PRISM_EXPORT int prism_attention_bf16_supported(int hd, int nh, int nkv) {
-    return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16;
+    return hd >= 16 && hd <= 128 && hd % 16 == 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16;
 }
+
+// one instantiation per head size
+#define PRISM_BY_HEAD_SIZE(hd, CALL)                   \
+    switch (hd) {                                      \
+        case 16: return CALL(16);                      \
+        case 32: return CALL(32);                      \
+        case 48: return CALL(48);                      \
+        case 64: return CALL(64);                      \
+        case 80: return CALL(80);                      \
+        case 96: return CALL(96);                      \
+        case 112: return CALL(112);                    \
+        case 128: return CALL(128);                    \
+    }                                                  \
+    return (int)cudaErrorInvalidValue
 
 // Decode: T tokens, one per request.  part_o: float [T, nh, nsplit, hd]; part_ml: float [T, nh, nsplit, 2].
 // With nsplit > 1 a second kernel merges the splits' partial results.
@@ -20,7 +36,9 @@ PRISM_EXPORT int prism_attention_decode_bf16(const void* q, int q_stride, void* 
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
              window, scale, part_o, part_ml, nsplit, err, stream
-    return hd == 64 ? prism::launch_decode<64>(ARGS) : prism::launch_decode<128>(ARGS);
+#define CALL(HD) prism::launch_decode<HD>(ARGS)
+    PRISM_BY_HEAD_SIZE(hd, CALL);
+#undef CALL
 #undef ARGS
 }
 
@@ -54,7 +72,9 @@ PRISM_EXPORT int prism_attention_decode_qkv_bf16(const float* parts, int ks, con
 #define ARGS (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
              window, scale, part_o, part_ml, nsplit, err, stream, &f
-    return hd == 64 ? prism::launch_decode<64>(ARGS) : prism::launch_decode<128>(ARGS);
+#define CALL(HD) prism::launch_decode<HD>(ARGS)
+    PRISM_BY_HEAD_SIZE(hd, CALL);
+#undef CALL
 #undef ARGS
 }
 
@@ -70,7 +90,9 @@ PRISM_EXPORT int prism_attention_prefill_bf16(const void* q, int q_stride, void*
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, seg_start, cached_len, S, max_q_len, nh, nkv, page_size, \
              num_pages, window, scale, err, stream
-    return hd == 64 ? prism::launch_prefill<64>(ARGS) : prism::launch_prefill<128>(ARGS);
+#define CALL(HD) prism::launch_prefill<HD>(ARGS)
+    PRISM_BY_HEAD_SIZE(hd, CALL);
+#undef CALL
 #undef ARGS
 }
 
@@ -80,11 +102,10 @@ PRISM_EXPORT int prism_attention_prefill_bf16(const void* q, int q_stride, void*
 PRISM_EXPORT int prism_attention_merge_bf16(const float* part_o, const float* part_ml, int nsplit, void* out,
                                             int out_stride, int T, int nh, int hd, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (nsplit < 1 || (hd != 64 && hd != 128)) return (int)cudaErrorInvalidValue;
-    // one thread per output element: the block size is the head size
-    if (hd == 64)
-        return (int)prism::launch_kernel(prism::attn_merge_kernel<64>, dim3(T * nh), dim3(64), 0, stream, part_o, part_ml,
-                                         nsplit, (__nv_bfloat16*)out, out_stride, nh);
-    return (int)prism::launch_kernel(prism::attn_merge_kernel<128>, dim3(T * nh), dim3(128), 0, stream, part_o, part_ml,
-                                     nsplit, (__nv_bfloat16*)out, out_stride, nh);
+    if (nsplit < 1 || hd < 16 || hd > 128 || hd % 16) return (int)cudaErrorInvalidValue;
+    // one thread per output element: the block is the head size rounded up to whole warps
+#define CALL(HD) (int)prism::launch_kernel(prism::attn_merge_kernel<HD>, dim3(T * nh), dim3((HD + 31) / 32 * 32), 0, stream, \
+                                           part_o, part_ml, nsplit, (__nv_bfloat16*)out, out_stride, nh)
+    PRISM_BY_HEAD_SIZE(hd, CALL);
+#undef CALL
 }

@@ -268,7 +268,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};     // odd k-steps: two shorter MMA chains
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ks += 2) {
+        for (int ks = 0; ks + 1 < HD / 16; ks += 2) {
             uint32_t b[4], b2[4];
             ldmatrix_x4(b, Ks + ((mat >> 1) * 8 + lr) * STRIDE + ks * 16 + (mat & 1) * 8);
             ldmatrix_x4(b2, Ks + ((mat >> 1) * 8 + lr) * STRIDE + (ks + 1) * 16 + (mat & 1) * 8);
@@ -276,6 +276,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
             mma_bf16_16816(s2[0], qf[ks + 1], b2[0], b2[1]);
             mma_bf16_16816(s2[1], qf[ks + 1], b2[2], b2[3]);
+        }
+        if ((HD / 16) & 1) {                      // an odd number of 16-wide k-steps (head sizes 16, 48, 80, 112): the last one
+            constexpr int ks = HD / 16 - 1;
+            uint32_t b[4];
+            ldmatrix_x4(b, Ks + ((mat >> 1) * 8 + lr) * STRIDE + ks * 16 + (mat & 1) * 8);
+            mma_bf16_16816(s[0], qf[ks], b[0], b[1]);
+            mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
@@ -402,7 +409,10 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
     const float* po = pdl_fresh(part_o) + (size_t)blockIdx.x * nsplit * HD;       // the attention kernel's output
     const float* pml = pdl_fresh(part_ml) + (size_t)blockIdx.x * nsplit * 2;
-    const int d = threadIdx.x;                                                    // blockDim.x == HD
+    // blockDim.x: HD rounded up to whole warps; a thread beyond HD (head sizes 16, 48, 80, 112) works on element
+    // 0 again and stores nothing
+    const bool mine = (int)threadIdx.x < HD;
+    const int d = mine ? threadIdx.x : 0;
     if (nsplit > MERGE_MAX_SPLITS) {
         float M = -INFINITY;
         for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
@@ -413,7 +423,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
             L += pml[2 * s + 1] * f;
             acc += po[(size_t)s * HD + d] * f;
         }
-        out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        if (mine) out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         return;
     }
     float v[MERGE_BATCH];
@@ -457,7 +467,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
         for (int i = 0; i < MERGE_BATCH; ++i)
             if (s0 + i < nsplit) acc += v[i] * s_w[s0 + i];
     }
-    out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(acc * s_inv);
+    if (mine) out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(acc * s_inv);
 }
 
 // ---------------------------------------------------------------------------
@@ -663,7 +673,7 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                                    scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, err,
                                    fused != nullptr ? *fused : DecodeQKV());
     if (rc != cudaSuccess || nsplit == 1) return (int)rc;
-    return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3(HD), 0, stream,
+    return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3((HD + 31) / 32 * 32), 0, stream,
                               (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);
 }
 

@@ -53,7 +53,8 @@ template <int HD> struct TileRow { static constexpr int STRIDE = HD + 8; };
 // is the same for K and V and is computed once.  Keys outside [lo, hi] are
 // zero-filled.  A page id outside the pool is reported and the row
 // zero-filled.  page_shift = log2(page_size) when that is a power of two, else -1.
-// THREADS threads (a CTA or one warp) load together; tid is the caller's index among them.
+// THREADS threads (a CTA or one warp) load together; tid is the caller's index among them.  Any head size
+// that is a multiple of 8: the (row, 16-byte chunk) pairs are dealt out to the threads in turn.
 template <int HD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* vs,
                                              const __nv_bfloat16* __restrict__ kcache,
@@ -62,11 +63,9 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
                                              int page_size, int page_shift, int num_pages, int nkv, int kvh,
                                              int* err, int tid) {
     constexpr int CHUNKS = HD / 8;                 // 16-byte chunks per row
-    constexpr int ROW_STEP = THREADS / CHUNKS;
-    static_assert(THREADS % CHUNKS == 0 && ROWS % ROW_STEP == 0, "tile shape");
-    const int c = tid % CHUNKS;                    // tid: index of this thread among the THREADS that load
+    constexpr int ITEMS = ROWS * CHUNKS;           // (row, chunk) pairs, dealt out to the threads in turn
     const size_t row_elems = (size_t)nkv * HD;
-    const size_t head_off = (size_t)kvh * HD + c * 8;
+    const size_t head_off = (size_t)kvh * HD;
     // Fast path: a tile that lies in one page and wholly inside [lo, hi]: one table lookup, then
     // rows at a constant stride.
     if (page_shift >= 0 && (first_key >> page_shift) == ((first_key + ROWS - 1) >> page_shift) && first_key >= lo &&
@@ -75,15 +74,17 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
         if (page >= 0 && page < num_pages) {
             const size_t base = ((size_t)page * page_size + (first_key & (page_size - 1))) * row_elems + head_off;
 #pragma unroll
-            for (int r = tid / CHUNKS; r < ROWS; r += ROW_STEP) {
-                cp_async16(ks + r * TileRow<HD>::STRIDE + c * 8, kcache + base + (size_t)r * row_elems, true);
-                cp_async16(vs + r * TileRow<HD>::STRIDE + c * 8, vcache + base + (size_t)r * row_elems, true);
+            for (int i = tid; i < ITEMS; i += THREADS) {
+                const int r = i / CHUNKS, c = i % CHUNKS;
+                cp_async16(ks + r * TileRow<HD>::STRIDE + c * 8, kcache + base + (size_t)r * row_elems + c * 8, true);
+                cp_async16(vs + r * TileRow<HD>::STRIDE + c * 8, vcache + base + (size_t)r * row_elems + c * 8, true);
             }
             return;
         }
     }
 #pragma unroll
-    for (int r = tid / CHUNKS; r < ROWS; r += ROW_STEP) {
+    for (int i = tid; i < ITEMS; i += THREADS) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
         const int key = first_key + r;
         bool valid = key >= lo && key <= hi;
         size_t off = 0;
@@ -100,7 +101,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
                 report_error(err, PRISM_ERR_PAGE_RANGE);
                 valid = false;
             } else {
-                off = ((size_t)page * page_size + in_page) * row_elems + head_off;
+                off = ((size_t)page * page_size + in_page) * row_elems + head_off + c * 8;
             }
         }
         cp_async16(ks + r * TileRow<HD>::STRIDE + c * 8, kcache + off, valid);

@@ -725,7 +725,7 @@ def decoders_apart(n_leading_single: int, their_max_kv_len: int, window: Optiona
 def attention_bf16_shape_ok(hd: int, nh: int, nkv: int) -> bool:
     """The rule of ``prism_attention_bf16_supported`` (csrc/attention_bf16.cu), for callers that have no
     library loaded (a model built on a host without a GPU)."""
-    return hd in (64, 128) and nkv > 0 and nh % nkv == 0 and nh // nkv <= 16
+    return 16 <= hd <= 128 and hd % 16 == 0 and nkv > 0 and nh % nkv == 0 and nh // nkv <= 16
 
 
 def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:

@@ -64,14 +64,14 @@ class GQAAttention(Mixer):
 
     def on_bound(self):
         # Said once, when the model is built, not found out from the step time: in bfloat16 the tensor-core
-        # attention kernels take head sizes 64 and 128 with up to 16 query heads per kv head; every other
-        # shape runs on the shape-generic kernel (one warp per token and head), correct but far slower.
+        # attention kernels take head sizes in steps of 16 up to 128 with up to 16 query heads per kv head; every
+        # other shape runs on the shape-generic kernel (one warp per token and head), correct but far slower.
         if self.dtype == torch.bfloat16 and not ops.attention_bf16_shape_ok(self.hd, self.nh, self.nkv):
             key = (self.hd, self.nh, self.nkv)
             if key not in _warned:
                 _warned.add(key)
                 warnings.warn(f"attention with head_dim {self.hd}, {self.nh} heads, {self.nkv} kv heads runs on the "
-                              f"shape-generic kernel in bfloat16 (the tensor-core kernels take head_dim 64 or 128 "
+                              f"shape-generic kernel in bfloat16 (the tensor-core kernels take head_dim 16, 32, ... 128 "
                               f"and up to 16 query heads per kv head): correct, but much slower", RuntimeWarning,
                               stacklevel=2)
 

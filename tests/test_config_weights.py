@@ -78,13 +78,17 @@ def test_sizes_no_kernel_takes_are_refused_when_the_model_is_built():
     build_model(dict(TINY_A, head_dim=256))
     import prism_b200.parts.attention as att
     att._warned.clear()
-    with pytest.warns(RuntimeWarning, match="shape-generic kernel"):
-        load_model_folder(model_folder("A"), "cpu", torch.bfloat16)          # head_dim 16
-    import warnings
-    with warnings.catch_warnings():
-        warnings.simplefilter("error")
-        load_model_folder(model_folder("A"), "cpu", torch.float32)           # float32 has one kernel: nothing to say
-        load_model_folder(model_folder("D"), "cpu", torch.bfloat16)          # head_dim 64: the tensor-core kernels
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        odd = write_model_folder(dict(TINY_A, hidden_size=72, head_dim=18), 0, d)         # head_dim 18: no multiple of 16
+        with pytest.warns(RuntimeWarning, match="shape-generic kernel"):
+            load_model_folder(odd, "cpu", torch.bfloat16)
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("error")
+            load_model_folder(odd, "cpu", torch.float32)                     # float32 has one kernel: nothing to say
+            load_model_folder(model_folder("A"), "cpu", torch.bfloat16)      # head_dim 16: the tensor-core kernels
+            load_model_folder(model_folder("D"), "cpu", torch.bfloat16)      # head_dim 64
 
 
 def test_registry():

@@ -490,6 +490,13 @@ DECODE_CASES = [
     (14, 2, 64, 256, None, [300, 17, 700, 64, 1] + [0] * 11, 9),        # a graph bucket of 16 with padded rows
     (14, 2, 64, 256, None, [300, 17, 700, 64, 1], 11),
     (12, 2, 128, 64, None, [129, 64, 1000, 0, 0, 0, 0, 0], 5),
+    # every head size in steps of 16 (an odd number of 16-wide steps: 16, 48, 80, 112)
+    (4, 2, 16, 16, None, [200, 15, 16, 0], 3),
+    (3, 1, 32, 8, None, [77, 300], 2),
+    (6, 3, 48, 16, 24, [23, 24, 25, 500], 4),
+    (10, 2, 80, 32, None, [1000, 31], 6),
+    (8, 8, 96, 64, None, [130, 64], 1),
+    (16, 1, 112, 256, None, [700, 257, 3], 5),
 ]
 
 
@@ -512,7 +519,7 @@ def test_attention_decode_bf16(case):
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
-@pytest.mark.parametrize("case", DECODE_CASES + [(8, 2, 64, 16, 40, [100, 39, 40, 41, 0], 3)])
+@pytest.mark.parametrize("case", DECODE_CASES + [(8, 2, 64, 16, 40, [100, 39, 40, 41, 0], 3)])     # head sizes 16 .. 128
 @pytest.mark.parametrize("bias_dtype", [None, torch.bfloat16, torch.float32])
 def test_attention_decode_finishes_the_qkv_projection(case, bias_dtype):
     """The decode kernel given the projection's partial sums instead of q and a filled cache: the same output
@@ -576,6 +583,12 @@ PREFILL_CASES = [
     (8, 8, 64, 16, None, [(0, 130), (17, 2)]),
     (16, 1, 64, 32, 50, [(0, 180), (49, 3), (50, 1), (400, 70)]),
     (14, 2, 128, 8, 64, [(100, 129), (0, 64)]),
+    (4, 2, 16, 16, None, [(0, 150), (20, 3)]),
+    (3, 1, 32, 8, None, [(5, 70), (0, 1)]),
+    (6, 3, 48, 16, 24, [(0, 100), (23, 2), (200, 65)]),
+    (10, 2, 80, 32, None, [(64, 64), (0, 130)]),
+    (8, 8, 96, 64, None, [(0, 200)]),
+    (16, 1, 112, 256, 300, [(250, 80), (0, 17)]),
 ]
 
 
