@@ -196,11 +196,27 @@ def register_toy():
                 cache.state[slot] = st
             return out.to(x.dtype)
 
+    @register_part("mixer", "toy_decay_on_device")
+    class ToyDecayOnDevice(ToyDecay):
+        """The same mixer for models that want their decode steps replayed from CUDA graphs: a step in
+        which every request brings one token is computed from the device's slot array alone (gather the
+        states, advance them, scatter them back), so nothing of it depends on the host's copy of the step."""
+        graph_safe = True
+
+        def forward(self, ctx, x, cache):
+            if not ctx.decode_only:
+                return super().forward(ctx, x, cache)
+            u = x.float() @ self.w["w_in"].float().T
+            slots = cache.slots.long()
+            st = DECAY * cache.state[slots] + u
+            cache.state.index_copy_(0, slots, st)          # padded rows of a graph all point at the spare slot
+            return st.to(x.dtype)
+
     def spec(cfg):
         H, V = cfg["hidden_size"], cfg["vocab_size"]
         norm = lambda p: PartSpec("rmsnorm", dict(width=H, eps=1e-5), prefix=p)
         ff = lambda p: PartSpec("swiglu", dict(hidden_size=H, intermediate_size=cfg["intermediate_size"]), prefix=p)
-        l0 = PartSpec("prenorm", dict(mixer=PartSpec("toy_decay", dict(hidden_size=H), prefix="l0.mix."),
+        l0 = PartSpec("prenorm", dict(mixer=PartSpec(cfg.get("mixer_kind", "toy_decay"), dict(hidden_size=H), prefix="l0.mix."),
                                       feed_forward=ff("l0.ff."), mixer_norm=norm("l0.n1."), ff_norm=norm("l0.n2.")))
         l1 = PartSpec("prenorm", dict(
             mixer=PartSpec("gqa_attention", dict(hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=16,
@@ -303,6 +319,19 @@ def test_toy_state_mixer_with_cuda_graphs_requested():
             ref = toy_plain(t, seq)
             for pos in range(len(seq)):
                 assert float((got[(rid, pos)] - ref[pos]).abs().max()) < 5e-5, (rid, pos)
+        # the variant of the mixer that works from the device's slot array declares itself safe: graphs are captured
+        with tempfile.TemporaryDirectory() as d2:
+            write_model_folder(dict(raw, mixer_kind="toy_decay_on_device"), 11, d2, store_dtype=torch.float32)
+            _, model2, pool2 = load_model_folder(d2, DEV, torch.float32)
+            runner2 = ModelRunner(model2, DEV, torch.float32, 8, trace_budget(steps, 8) // 8, 4, use_cuda_graph=True,
+                                  graph_batch_sizes=(1, 2))
+            assert runner2.graph_safe and runner2.use_cuda_graph
+            got2 = run_trace(runner2, steps)
+            assert runner2._graphs and runner2.graph_kernel_launches > 0
+            for rid, seq in seqs.items():
+                ref = toy_plain(t, seq)
+                for pos in range(len(seq)):
+                    assert float((got2[(rid, pos)] - ref[pos]).abs().max()) < 5e-5, (rid, pos)
     # the stock attention model keeps its graphs
     from helpers import model_folder
     _, m2, pool2 = load_model_folder(model_folder("A"), DEV, torch.float32)
