@@ -10,9 +10,12 @@ from helpers import (TINY, compare_with_plain, model_folder, random_tokens, run_
 pytestmark = pytest.mark.gpu
 
 # float32: the engine and the plain model differ by the order of float32 additions only.
-# bfloat16: activations are rounded to 8 bits of mantissa where they are stored
-# (norm out, qkv, attention out, SwiGLU out); weights are the same bf16 values on both sides.
-TOL = {"float32": dict(atol=2e-5, rtol=1e-5), "bfloat16": dict(atol=2e-3, rtol=3e-2)}
+# bfloat16: activations are rounded to 8 bits of mantissa where they are stored (norm out, qkv, attention
+# out, SwiGLU out); weights are the same bf16 values on both sides.  The yardstick is what that rounding alone
+# does to the plain model's logits of the same sequence (helpers.plain_rounding_error, about 3e-3 at a logit
+# scale of 1): the engine measured 0.76 to 1.38 times that in every configuration and every way of cutting,
+# and may be at most twice it.  (A constant bound would have to be ten times looser to hold everywhere.)
+TOL = {"float32": dict(atol=2e-5, rtol=1e-5), "bfloat16": dict(rounding_slack=2.0)}
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 71, 130], "C": [3, 30, 64, 97, 150], "D": [2, 65, 128, 200, 333]}
 
 
@@ -141,8 +144,10 @@ def test_tensors_stored_in_float32_under_the_bf16_engine(which, tmp_path):
     got = run_trace(runner, steps)
     for rid, seq in seqs.items():
         ref = P.forward(pcfg, pt, list(seq))
-        scale = float(ref.abs().max())
+        # twice what rounding the stored activations to bfloat16 does to this model's own logits
+        bound = TOL["bfloat16"]["rounding_slack"] * float(
+            (P.forward(pcfg, pt, list(seq), store=lambda v: v.bfloat16().float()) - ref).abs().max())
         for pos in range(len(seq)):
             err = float((got[(rid, pos)] - ref[pos]).abs().max())
-            assert err <= TOL["bfloat16"]["atol"] + TOL["bfloat16"]["rtol"] * scale, (rid, pos, err)
+            assert err <= bound, (rid, pos, err, bound)
     assert len(got) == sum(len(s) for s in seqs.values())
