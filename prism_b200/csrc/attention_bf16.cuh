@@ -29,6 +29,7 @@ constexpr int ATT_THREADS = 128;   // 4 warps
 #define PRISM_DEC_STAGES 3
 #endif
 constexpr int DEC_STAGES = PRISM_DEC_STAGES;
+constexpr int DEC_MIN_TILES = 3;   // tiles a split keeps at least: shorter CTAs cost more in fixed latencies than they share
 constexpr int PRE_STAGES = 2;
 constexpr int PRE_ROWS = 64;       // query rows per CTA
 
@@ -127,7 +128,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int hi = pos;
     const int first_tile = lo / ATT_TILE, ntiles = hi / ATT_TILE - first_tile + 1;
-    const int per_split = (ntiles + nsplit - 1) / nsplit;
+    // nsplit is chosen for the longest context the launch may meet (a captured graph knows a bound only): a
+    // shorter one is shared among fewer CTAs, DEC_MIN_TILES tiles each at least, and the rest leave empty partials
+    const int per_split = max((ntiles + nsplit - 1) / nsplit, nsplit > 1 ? DEC_MIN_TILES : 1);
     const int t0 = first_tile + split * per_split;
     const int t1 = min(t0 + per_split, first_tile + ntiles);
 
@@ -461,8 +464,10 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
     for (int i = 0; i < MERGE_BATCH; ++i)
         if (i < nsplit) acc += v[i] * s_w[i];
     for (int s0 = MERGE_BATCH; s0 < nsplit; s0 += MERGE_BATCH) {
+        // splits that saw no key (a launch sized for a longer context) have weight 0: nothing is asked of them
 #pragma unroll
-        for (int i = 0; i < MERGE_BATCH; ++i) v[i] = s0 + i < nsplit ? po[(size_t)(s0 + i) * HD + d] : 0.f;
+        for (int i = 0; i < MERGE_BATCH; ++i)
+            v[i] = (s0 + i < nsplit && s_w[s0 + i] != 0.f) ? po[(size_t)(s0 + i) * HD + d] : 0.f;
 #pragma unroll
         for (int i = 0; i < MERGE_BATCH; ++i)
             if (s0 + i < nsplit) acc += v[i] * s_w[s0 + i];

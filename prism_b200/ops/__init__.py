@@ -732,6 +732,7 @@ def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
     return bool(lib().prism_attention_bf16_supported(hd, nh, nkv))
 
 
+DECODE_MIN_TILES = 3                # 64-key tiles a split CTA keeps at least (csrc/attention_bf16.cuh: DEC_MIN_TILES)
 DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what the balance gains (batch 64: 8,192 keys
                                     # 203 -> 201 us in 4 splits, 32,768 keys 717 -> 673 us)
 
@@ -739,18 +740,21 @@ DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what t
 def decode_splits(T: int, nkv: int, max_kv_len: int, window: Optional[int], balance: bool = True,
                   sms: Optional[int] = None) -> int:
     """How many CTAs share one (token, kv head)'s keys: as many as fill one wave
-    of two CTAs per SM, at most one per 64-key tile.  More, shorter CTAs lose:
-    each pays the same fixed latencies (position, block table, first bytes, merge).  ``max_kv_len`` is the
-    longest context of the batch, or, when a graph is captured, the longest the graph may ever see;
-    ``balance`` (the few splits of a large batch against long contexts) is for the former only: a bound
-    of 32,768 says nothing about the contexts a replay will meet."""
-    if os.environ.get("PRISM_DECODE_SPLITS"):
+    of two CTAs per SM, at most one per ``DECODE_MIN_TILES`` 64-key tiles.  More, shorter CTAs lose:
+    each pays the same fixed latencies (position, block table, first bytes, merge), and the merge grows
+    with them (batch 1 at 2,100 keys: 33 splits of one tile 2.90 ms a step, 12 splits 2.81, 8 splits 2.87).
+    ``max_kv_len`` is the longest context of the batch, or, when a graph is captured, the longest the
+    graph may ever see - the kernel itself keeps ``DECODE_MIN_TILES`` tiles per CTA for the context it
+    finds and leaves the splits it does not need empty.  ``balance`` (the few splits of a large batch
+    against long contexts) is for the former only: a bound of 32,768 says nothing about the contexts a
+    replay will meet."""
+    if os.environ.get("PRISM_DECODE_SPLITS", "0") != "0":
         return int(os.environ["PRISM_DECODE_SPLITS"])
     NUM_SMS = sms or num_sms()
     span = min(max_kv_len, window + 64) if window else max_kv_len
     tiles = max(1, (span + 63) // 64)
     fill = (2 * NUM_SMS) // max(1, T * nkv)
-    n = max(1, min(tiles, 64, fill))
+    n = max(1, min(-(-tiles // DECODE_MIN_TILES), 64, fill))
     if balance and n == 1 and tiles >= DECODE_BALANCE_FROM_TILES:
         # A large batch against long contexts: one CTA per (token, kv head) fills the GPU, but unevenly (256
         # CTAs are two on 108 SMs and one on 40, and the kernel lasts as long as the pairs).  A few splits

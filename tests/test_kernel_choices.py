@@ -24,7 +24,10 @@ def test_decode_splits_choice():
     """As many splits as fill one wave; a batch that fills the GPU unevenly gets a few splits once the
     contexts are long enough to pay for the merge."""
     assert ops.decode_splits(8, 4, 2100, None, sms=B200) == 9                  # 288 CTAs for 296 places
-    assert ops.decode_splits(1, 4, 2100, None, sms=B200) == 33                 # one per 64-key tile
+    assert ops.decode_splits(1, 4, 2100, None, sms=B200) == 11                 # three 64-key tiles each at least
+    assert ops.decode_splits(1, 4, 500, None, sms=B200) == 3
+    assert ops.decode_splits(1, 4, 100, None, sms=B200) == 1
+    assert ops.decode_splits(1, 4, 32768, None, sms=B200) == 64                # never more than 64
     assert ops.decode_splits(64, 4, 2100, None, sms=B200) == 1                 # short contexts: no merge
     assert ops.decode_splits(64, 4, 8192, None, sms=B200) == 1
     assert ops.decode_splits(64, 4, 32768, None, sms=B200) == 4                # 256 CTAs would be 2 + 1 per SM
