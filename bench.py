@@ -149,7 +149,11 @@ def result_line(args, cfg, layers_model, pk, B, ms, ctx_mean, prefill_ms, points
                     "frac": round(pf_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points,
+        # decode at batch 1 and 64: tokens a second, and beside them the step time and the fraction of the
+        # measured copy bandwidth (weights once + the live requests' keys and values over the step time)
+        "points": {k: v["value"] for k, v in points.items()},
+        "points_ms": {k: v["ms"] for k, v in points.items()},
+        "points_frac": {k: v["frac"] for k, v in points.items()},
     }
     if impl:
         out["impl"] = impl
