@@ -296,13 +296,22 @@ def tc_gemm_ok(x: torch.Tensor, w: torch.Tensor, max_m: Optional[int] = None) ->
             and bool(lib().prism_gemm_tcgen05_supported(M, w.shape[0], K)))
 
 
-def tc_ksplit(N: int, K: int, sms: Optional[int] = None) -> int:
+def tc_ksplit(N: int, K: int, sms: Optional[int] = None, M: Optional[int] = None) -> int:
     """CTAs that share one 128-row tile's K range: about one CTA per SM in all (``sms``: the device's
-    count), at least 8 blocks of 64 k each."""
+    count), at least 8 blocks of 64 k each.  With up to 16 tokens (``M``) two of the kernel's CTAs fit on an
+    SM, and a product with a long K (the down projection) is shared half as finely again, 32 blocks each at
+    least: the CTAs that double up have twice the weights on their way before the dependency wait (7B
+    down projection, 5 -> 7 splits: 3.008 -> 2.992 ms a step at batch 8, 2.831 -> 2.804 at batch 1, 3.218 ->
+    3.181 at batch 16; with 32 tokens and more one CTA fills an SM's shared memory and 5 stays best)."""
     tiles = (N + 127) // 128
     if TC_KSPLIT_FORCED:
         return TC_KSPLIT_FORCED
-    return max(1, min((sms or num_sms()) // tiles, ((K + 63) // 64) // 8))
+    n_sms = sms or num_sms()
+    kblocks = (K + 63) // 64
+    ks = max(1, min(n_sms // tiles, kblocks // 8))
+    if M is not None and M <= 16 and kblocks // ks >= 48:
+        ks = max(ks, min((3 * n_sms // 2) // tiles, kblocks // 32))
+    return ks
 
 
 def check_tc_errors():
@@ -320,7 +329,7 @@ def linear_delta(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     of partial sums over K, which the fused add + norm kernel adds up."""
     if bias is None and tc_gemm_ok(x, w):
         N, K = w.shape
-        ks = tc_ksplit(N, K)
+        ks = tc_ksplit(N, K, M=x.shape[0])
         if ks > 1:
             out = torch.empty((ks, x.shape[0], N), dtype=torch.float32, device=x.device)
             gemm_tc(x, w, None, out, EPI_PARTIAL, ksplit=ks)
