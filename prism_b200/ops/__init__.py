@@ -299,17 +299,20 @@ def tc_gemm_ok(x: torch.Tensor, w: torch.Tensor, max_m: Optional[int] = None) ->
 def tc_ksplit(N: int, K: int, sms: Optional[int] = None, M: Optional[int] = None) -> int:
     """CTAs that share one 128-row tile's K range: about one CTA per SM in all (``sms``: the device's
     count), at least 8 blocks of 64 k each.  With up to 16 tokens (``M``) two of the kernel's CTAs fit on an
-    SM, and a product with a long K (the down projection) is shared half as finely again, 32 blocks each at
-    least: the CTAs that double up have twice the weights on their way before the dependency wait (7B
-    down projection, 5 -> 7 splits: 3.008 -> 2.992 ms a step at batch 8, 2.831 -> 2.804 at batch 1, 3.218 ->
-    3.181 at batch 16; with 32 tokens and more one CTA fills an SM's shared memory and 5 stays best)."""
+    SM, so the count is rounded to the nearest instead of down (14B qkv projection, 56 tiles: 3 splits = 168
+    CTAs instead of 2 = 112: 6.003 -> 5.880 ms a step at batch 8), and a product with a long K (the down
+    projection) is shared half as finely again, 32 blocks each at least: the CTAs that double up have twice
+    the weights on their way before the dependency wait (7B down projection, 5 -> 7 splits: 3.008 -> 2.992 ms
+    a step at batch 8, 2.831 -> 2.804 at batch 1, 3.218 -> 3.181 at batch 16; 14B and 32B steps 1.9 % shorter).
+    With 32 tokens and more one CTA fills an SM's shared memory: never more CTAs than SMs."""
     tiles = (N + 127) // 128
     if TC_KSPLIT_FORCED:
         return TC_KSPLIT_FORCED
     n_sms = sms or num_sms()
     kblocks = (K + 63) // 64
-    ks = max(1, min(n_sms // tiles, kblocks // 8))
-    if M is not None and M <= 16 and kblocks // ks >= 48:
+    few = M is not None and M <= 16
+    ks = max(1, min((2 * n_sms + tiles) // (2 * tiles) if few else n_sms // tiles, kblocks // 8))
+    if few and kblocks // ks >= 48:
         ks = max(ks, min((3 * n_sms // 2) // tiles, kblocks // 32))
     return ks
 
@@ -473,7 +476,7 @@ def qkv_rotate_store(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[
     kc, vc = (cache.k, cache.v) if cache.write else (None, None)
     rd = rot.rotary_dim if rot is not None else 0
     if QKV_PARTIAL and table is not None and tc_gemm_ok(x, qkv_w) and hd % 8 == 0 and rot.rotary_dim % 16 == 0:
-        ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
+        ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1], M=T)
         if ks > 1:
             parts = ctx.alloc((ks, T, qs + 2 * kvs), torch.float32)
             gemm_tc(x, qkv_w, None, parts, EPI_PARTIAL, ksplit=ks)
@@ -865,7 +868,7 @@ def qkv_attention(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[tor
             and rot.rotary_dim == hd and x.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
             and not FORCE_GENERIC_ATTENTION and tc_gemm_ok(x, qkv_w)
             and cache.k.is_contiguous() and cache.v.is_contiguous() and attention_bf16_supported(hd, nh, nkv)):
-        ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1])
+        ks = tc_ksplit(qkv_w.shape[0], qkv_w.shape[1], M=T)
         if ks > 1:
             key = ("rotary_table", rot.inv_freq.data_ptr())          # one table per step for all layers
             table = ctx.scratch.get(key)

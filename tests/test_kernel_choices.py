@@ -47,6 +47,9 @@ def test_grids_follow_the_device():
     # a few tokens and a long K: half as many CTAs again (two fit on an SM), 32 k-blocks each at least
     assert ops.tc_ksplit(3584, 18944, sms=148, M=8) == 7 and ops.tc_ksplit(3584, 18944, sms=148, M=32) == 5
     assert ops.tc_ksplit(4608, 3584, sms=148, M=8) == 4 and ops.tc_ksplit(5120, 13824, sms=148, M=1) == 5
+    # few tokens: rounded to the nearest count, not down (two CTAs fit on an SM); many tokens: never more CTAs than SMs
+    assert ops.tc_ksplit(7168, 5120, sms=148, M=8) == 3 and ops.tc_ksplit(7168, 5120, sms=148, M=32) == 2
+    assert ops.tc_ksplit(5120, 5120, sms=148, M=1) == 4 and ops.tc_ksplit(3584, 3584, sms=148, M=16) == 5
     assert ops.prefill_splits(1, 128, 28, 32768 + 128, None, sms=64) < ops.prefill_splits(1, 128, 28, 32768 + 128, None, sms=148)
     import torch
     if not torch.cuda.is_available():
