@@ -39,7 +39,8 @@ class EngineConfig:
     """Cache and execution knobs (engine/config.py:24-31)."""
     gpu_id: int = 0
     kv_page_size: int = 64              # tokens per page
-    num_pages: Optional[int] = None     # explicit pool size per cache group, or
+    num_pages: Optional[int] = None     # explicit pool size of the groups that keep all keys (windowed groups get what
+                                        # their window needs, never more than this; cache.manager.pool_sizes), or
     kv_cache_budget_gb: float = 35.0    # ... derived from this budget (engine/scheduler.py:100-103)
     max_seq_len: Optional[int] = None   # block-table width; default max_position_embeddings
     use_cuda_graph: bool = True
