@@ -104,6 +104,18 @@ __device__ __forceinline__ void rotate4(const float (&x1)[4], const float (&x2)[
     hi = make_uint2(pack_bf16(y2[0], y2[1]), pack_bf16(y2[2], y2[3]));
 }
 
+// How many CTAs share the keys of one (token, kv head) when the step's descriptor carries a plan: the host
+// has looked for the smallest number of 64-key tiles per CTA (`target_x16`, in sixteenths) with which the CTAs
+// of all decoding requests together still fit on the GPU at once.  A request then gets as many CTAs as keep
+// each of them at or below the target - a long context many, a short one a single CTA - so that no CTA of a
+// ragged batch runs much longer than the others; never so many that one keeps fewer than DEC_MIN_TILES tiles,
+// at most `cap` (the grid's extent).  The same few integer operations run on the host (ops.decode_used_splits).
+__device__ __forceinline__ int decode_used_splits(int ntiles, int target_x16, int cap) {
+    const int target = max(target_x16, DEC_MIN_TILES * 16);                 // a descriptor without a plan holds 0
+    const int u = min((ntiles * 16 + target - 1) / target, ntiles / DEC_MIN_TILES);
+    return min(max(u, 1), cap);
+}
+
 template <int HD, bool FUSED = false>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -112,7 +124,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh,
                    int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit,
-                   __nv_bfloat16* __restrict__ out, int out_stride, int* err, const DecodeQKV fq) {
+                   __nv_bfloat16* __restrict__ out, int out_stride, int* err, const DecodeQKV fq,
+                   const int* __restrict__ plan) {
     __shared__ __align__(16) __nv_bfloat16 s_own_kv[FUSED ? 2 * HD : 8];     // FUSED: this step's own key and value
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int SUB_ELEMS = 16 * STRIDE;                           // one warp's 16 keys of a tile
@@ -130,7 +143,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int first_tile = lo / ATT_TILE, ntiles = hi / ATT_TILE - first_tile + 1;
     // nsplit is chosen for the longest context the launch may meet (a captured graph knows a bound only): a
     // shorter one is shared among fewer CTAs, DEC_MIN_TILES tiles each at least, and the rest leave empty partials
-    const int per_split = max((ntiles + nsplit - 1) / nsplit, nsplit > 1 ? DEC_MIN_TILES : 1);
+    int per_split = max((ntiles + nsplit - 1) / nsplit, nsplit > 1 ? DEC_MIN_TILES : 1);
+    if (plan != nullptr) {
+        // the step's plan (part of its descriptor, complete before the step's first kernel): this request's
+        // share of the CTAs follows its own length; the CTAs beyond it have nothing to do and leave nothing
+        const int used = decode_used_splits(ntiles, plan[0], nsplit);
+        if (split >= used) return;
+        per_split = (ntiles + used - 1) / used;
+    }
     const int t0 = first_tile + split * per_split;
     const int t1 = min(t0 + per_split, first_tile + ntiles);
 
@@ -402,16 +422,25 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 constexpr int MERGE_BATCH = 16;
 constexpr int MERGE_MAX_SPLITS = 256;      // weights kept in shared memory; more splits than this take the slow loop
 
+// `plan` (with `positions`, `window`): the decode kernel ran under a plan, only the first
+// decode_used_splits(...) partials of a token exist; `cap` is the partial arrays' extent.
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  int nsplit, __nv_bfloat16* __restrict__ out, int out_stride, int nh) {
+                                  int cap, __nv_bfloat16* __restrict__ out, int out_stride, int nh,
+                                  const int* __restrict__ plan, const int* __restrict__ positions, int window) {
     __shared__ float s_w[MERGE_MAX_SPLITS];
     __shared__ float s_inv;
     pdl_trigger();
-    pdl_wait();
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
-    const float* po = pdl_fresh(part_o) + (size_t)blockIdx.x * nsplit * HD;       // the attention kernel's output
-    const float* pml = pdl_fresh(part_ml) + (size_t)blockIdx.x * nsplit * 2;
+    int nsplit = cap;
+    if (plan != nullptr) {
+        const int pos = positions[t];
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        nsplit = decode_used_splits(pos / ATT_TILE - lo / ATT_TILE + 1, plan[0], cap);
+    }
+    pdl_wait();
+    const float* po = pdl_fresh(part_o) + (size_t)blockIdx.x * cap * HD;          // the attention kernel's output
+    const float* pml = pdl_fresh(part_ml) + (size_t)blockIdx.x * cap * 2;
     // blockDim.x: HD rounded up to whole warps; a thread beyond HD (head sizes 16, 48, 80, 112) works on element
     // 0 again and stores nothing
     const bool mine = (int)threadIdx.x < HD;
@@ -668,7 +697,7 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
                   const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
                   int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
-                  int* err, cudaStream_t stream, const DecodeQKV* fused = nullptr) {
+                  int* err, cudaStream_t stream, const DecodeQKV* fused = nullptr, const int* plan = nullptr) {
     static_assert(dec_smem<HD>() >= (size_t)(4 * 16 * HD + 128) * sizeof(float), "merge scratch must fit");
     dim3 grid(nsplit, nkv, T);
     auto kern = fused != nullptr ? attn_decode_kernel<HD, true> : attn_decode_kernel<HD, false>;
@@ -676,10 +705,11 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
     cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
                                    positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
                                    scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, err,
-                                   fused != nullptr ? *fused : DecodeQKV());
+                                   fused != nullptr ? *fused : DecodeQKV(), plan);
     if (rc != cudaSuccess || nsplit == 1) return (int)rc;
     return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3((HD + 31) / 32 * 32), 0, stream,
-                              (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh);
+                              (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh, plan, positions,
+                              window);
 }
 
 template <int HD>

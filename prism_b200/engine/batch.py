@@ -9,7 +9,12 @@ cache, described by int32 arrays that are packed on the host in pinned memory
 and reach the device in one copy:
 
     token_ids[T] positions[T] tok_seg[T] seg_start[S+1] cached_len[S]
-    q_len[S] state_slots[S] logit_rows[R] block_tables[G][S, W]
+    q_len[S] state_slots[S] logit_rows[R] decode_plan[G] block_tables[G][S, W]
+
+``decode_plan[g]`` is one number per paged cache group for the decode attention
+kernel: how many 64-key tiles a CTA should take (in sixteenths), from the
+contexts of the step's decoding requests, so that a ragged batch is shared
+among equally loaded CTAs (``ops.decode_split_target``); 0: no plan.
 """
 
 from __future__ import annotations
@@ -44,7 +49,7 @@ class BatchLayout:
         self.off = {}
         for name, n in (("token_ids", self.T), ("positions", self.T), ("tok_seg", self.T),
                         ("seg_start", self.S + 1), ("cached_len", self.S), ("q_len", self.S),
-                        ("state_slots", self.S), ("logit_rows", self.R)):
+                        ("state_slots", self.S), ("logit_rows", self.R), ("decode_plan", len(self.paged_groups))):
             self.off[name] = (o, n)
             o += (n + 3) // 4 * 4               # keep every array 16-byte aligned
         for g in self.paged_groups:
@@ -76,16 +81,21 @@ class StepContext:
         self.seg_start, self.cached_len, self.q_len = v("seg_start"), v("cached_len"), v("q_len")
         self.state_slots, self.logit_rows = v("state_slots"), v("logit_rows")
         self.block_tables = {g: v(f"bt{g}").view(layout.S, layout.W) for g in layout.paged_groups}
+        plan = v("decode_plan")
+        self.decode_plan = {g: plan[i:i + 1] for i, g in enumerate(layout.paged_groups)}    # device, one int per group
+        self.split_caps = {}       # group -> most CTAs per (token, kv head) under the plan (host side); empty: no plan
 
     def alloc(self, shape, dtype):
         return torch.empty(shape, dtype=dtype, device=self.device)
 
 
 def pack_batch(layout: BatchLayout, token_ids, positions, tok_seg, seg_start, cached_len, q_len,
-               slots, logit_rows, block_rows: Dict[int, List[List[int]]], pad_page: Dict[int, int]):
+               slots, logit_rows, block_rows: Dict[int, List[List[int]]], pad_page: Dict[int, int],
+               decode_plan: Optional[Dict[int, int]] = None):
     """Fill a pinned int32 tensor with the descriptor.  ``block_rows[g][s]`` is
     request s's logical-page -> physical-page list in group g; entries beyond
-    it (and pages already given back) read ``pad_page[g]``, the scratch page."""
+    it (and pages already given back) read ``pad_page[g]``, the scratch page.
+    ``decode_plan[g]``: the decode kernel's tiles-per-CTA target of group g (absent: 0)."""
     host = torch.empty(layout.total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
     a = host.numpy()
     a[:] = 0
@@ -95,6 +105,9 @@ def pack_batch(layout: BatchLayout, token_ids, positions, tok_seg, seg_start, ca
         o, n = layout.off[name]
         if n:
             a[o:o + n] = np.asarray(vals, dtype=np.int32)
+    if decode_plan:
+        o, n = layout.off["decode_plan"]
+        a[o:o + n] = np.asarray([decode_plan.get(g, 0) for g in layout.paged_groups], dtype=np.int32)
     for g in layout.paged_groups:
         o, n = layout.off[f"bt{g}"]
         bt = a[o:o + n].reshape(layout.S, layout.W)

@@ -16,6 +16,7 @@ position 0 and the scratch page and their logits are dropped.
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Sequence
 
 import torch
@@ -69,7 +70,9 @@ class ModelRunner:
             for m in model.walk() if isinstance(m, Mixer))
         self.use_cuda_graph = bool(use_cuda_graph) and self.graph_safe
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]
-        self._graphs: Dict[int, dict] = {}
+        from .. import ops
+        self._sms = ops.num_sms(self.device)
+        self._graphs: Dict[tuple, dict] = {}     # (bucket, decode grid extents) -> captured step
         self.graph_kernel_launches = 0       # kernels of this library replayed inside graphs
         self.last_h2d_bytes = 0              # bytes of the last step's batch descriptor (host to device)
 
@@ -131,12 +134,13 @@ class ModelRunner:
         host_meta = dict(seg_start=seg_start, cached_len=cached, q_len=qlen, slots=slots, tok_seg=seg_of)
 
         S = len(segments)
+        plan, caps = self._decode_plan(cached, qlen)
         if self.use_cuda_graph and max_q == 1 and S <= self.graph_batch_sizes[-1]:
-            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows, token_source)
+            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows, token_source, plan, caps)
         else:
             layout = BatchLayout(len(tok), S, len(rows), self.cache.table_width, self.paged_groups)
             host = pack_batch(layout, tok, pos, seg_of, seg_start, cached, qlen, slots, rows,
-                              block_rows, self.pad_page)
+                              block_rows, self.pad_page, plan)
             dev = host.to(self.device, non_blocking=True)
             self.last_h2d_bytes = host.numel() * 4
             if token_source is not None:
@@ -144,11 +148,29 @@ class ModelRunner:
                 layout.view(dev, "token_ids").copy_(token_source[:S], non_blocking=True)
             ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions,
                               host_meta, max_q, max_kv)
+            ctx.split_caps = caps
             views = self.storage.views(ctx.block_tables, ctx.state_slots, slots)
             logits = self.model.forward(ctx, views)
         for s in segments:
             self.cache.commit(s.req_id, len(s.tokens))
         return logits
+
+    def _decode_plan(self, cached, qlen):
+        """The decode attention kernel's plan for the single-token segments at the head of the batch, per
+        paged cache group: ``({group: tiles per CTA in sixteenths}, {group: most CTAs a request gets})``,
+        from the requests' own contexts, so that a long context among short ones is shared among many CTAs
+        (``ops.decode_plan_for``).  Empty when the batch starts with a prompt portion."""
+        from .. import ops
+        lead = 0
+        while lead < len(qlen) and qlen[lead] == 1:
+            lead += 1
+        if not lead or os.environ.get("PRISM_DECODE_SPLITS", "0") != "0":
+            return {}, {}
+        plan, caps = {}, {}
+        for g in self.paged_groups:
+            need = self.groups[g].need
+            plan[g], caps[g] = ops.decode_plan_for(cached[:lead], need.num_kv_heads, need.window, self._sms)
+        return plan, caps
 
     # ---- decode graphs ---------------------------------------------------------------
     def _bucket(self, n: int) -> int:
@@ -157,9 +179,24 @@ class ModelRunner:
                 return b
         raise ValueError(n)
 
-    def _capture(self, B: int) -> dict:
+    def _graph_caps(self, B: int, caps: Dict[int, int]) -> tuple:
+        """The grid extent of the decode attention kernel is part of a captured graph, so a bucket has one
+        graph per extent, and the extents are few: powers of two and the one that fills the GPU with B
+        requests (what a batch of equal, long contexts asks for).  The smallest that holds what the plan
+        wants; the kernel leaves the CTAs a request does not use empty."""
+        out = []
+        for g in self.paged_groups:
+            need = self.groups[g].need
+            fill = max(1, min(64, (2 * self._sms) // max(1, B * need.num_kv_heads)))
+            want = caps.get(g, fill)
+            out.append(min(c for c in sorted({1, 2, 4, 8, 16, 32, 64, fill}) if c >= min(want, 64)))
+        return tuple(out)
+
+    def _capture(self, B: int, caps: tuple) -> dict:
         """Capture the decode step for a bucket of B one-token segments: static
-        descriptor buffer, every row's logits computed."""
+        descriptor buffer, every row's logits computed.  ``caps``: the decode attention
+        kernel's grid extent for each paged group (``_graph_caps``)."""
+        split_caps = dict(zip(self.paged_groups, caps))
         layout = BatchLayout(B, B, B, self.cache.table_width, self.paged_groups)
         dev = torch.zeros(layout.total, dtype=torch.int32, device=self.device)
         pad_rows = {g: [[] for _ in range(B)] for g in self.paged_groups}
@@ -171,6 +208,7 @@ class ModelRunner:
             # rotary table) must be produced inside the capture, in the graph's own memory
             c = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions, None,
                             1, self.max_seq_len)
+            c.split_caps = split_caps
             return c, self.storage.views(c.block_tables, c.state_slots, None)
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -188,18 +226,19 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         return dict(graph=graph, layout=layout, dev=dev, out=out, launches=ops.launch_count - before)
 
-    def _step_graph(self, tok, pos, cached, slots, rows, block_rows, token_source=None):
+    def _step_graph(self, tok, pos, cached, slots, rows, block_rows, token_source=None, plan=None, caps=None):
         S = len(tok)
         B = self._bucket(S)
-        g = self._graphs.get(B)
+        key = (B, self._graph_caps(B, caps or {}))
+        g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[B] = self._capture(B)
+            g = self._graphs[key] = self._capture(*key)
         pad = B - S
         scratch_slot = self.cache.max_seqs
         br = {k: v + [[] for _ in range(pad)] for k, v in block_rows.items()}
         host = pack_batch(g["layout"], tok + [0] * pad, pos + [0] * pad, list(range(B)), list(range(B + 1)),
                           cached + [0] * pad, [1] * B, slots + [scratch_slot] * pad, list(range(B)),
-                          br, self.pad_page)
+                          br, self.pad_page, plan)
         g["dev"].copy_(host, non_blocking=True)
         self.last_h2d_bytes = host.numel() * 4
         if token_source is not None:
@@ -214,11 +253,13 @@ class ModelRunner:
         return out[torch.tensor(rows, device=self.device)]
 
     def warmup_graphs(self, sizes: Optional[Sequence[int]] = None) -> None:
-        """Capture the decode graphs ahead of time (executor.py:312-318)."""
+        """Capture the decode graphs ahead of time (executor.py:312-318): for every bucket the graph
+        that a batch of long contexts uses; those for short or ragged contexts follow at their first use."""
         if self.use_cuda_graph:
             for b in sizes or self.graph_batch_sizes:
-                if b not in self._graphs and b <= self.graph_batch_sizes[-1]:
-                    self._graphs[b] = self._capture(b)
+                key = (b, self._graph_caps(b, {}))
+                if key not in self._graphs and b <= self.graph_batch_sizes[-1]:
+                    self._graphs[key] = self._capture(*key)
 
     def invalidate_graphs(self) -> None:
         self._graphs.clear()

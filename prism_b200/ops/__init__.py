@@ -29,6 +29,7 @@ import os
 import threading
 from typing import Optional
 
+import numpy as np
 import torch
 
 from ..csrc import build as _build
@@ -91,9 +92,9 @@ class _Sig:
                                _i, _f, _p, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
-                                   _p, _p, _i, _p, _p]
+                                   _p, _p, _i, _p, _p, _p]
     prism_attention_decode_qkv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
-                                       _i, _f, _p, _p, _i, _p, _p]
+                                       _i, _f, _p, _p, _i, _p, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
     prism_attention_prefill_tc_supported = [_i, _i, _i, _i]
@@ -578,11 +579,14 @@ QKV_PARTIAL = os.environ.get("PRISM_QKV_PARTIAL", "1") != "0"
 
 
 def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
-                          scale, nsplit, part_o, part_ml, err):
+                          scale, nsplit, part_o, part_ml, err, plan: Optional[torch.Tensor] = None):
     """Tensor-core decode attention (one token per request) with the keys split
     over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
-    ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results."""
-    _cuda(q, out, k_cache, v_cache, block_table, positions, tok_seg, part_o, part_ml)
+    ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results.
+    ``plan`` (device int32, one element: ``decode_split_target`` of the step): every
+    token's keys are then shared among ``decode_used_splits`` CTAs of its own, at most
+    ``nsplit``, and the rest of the grid returns at once."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, tok_seg, part_o, part_ml, plan)
     T, nh, hd = q.shape
     nkv, P = k_cache.shape[2], k_cache.shape[1]
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -593,14 +597,15 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                              _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                              int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                             int(nsplit), _ptr(err), _stream()), "attention_decode_bf16")
+                                             int(nsplit), _ptr(plan), _ptr(err), _stream()), "attention_decode_bf16")
     if nsplit > 1:
         global launch_count
         launch_count += 1          # the merge kernel
 
 
 def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache, block_table, positions, tok_seg,
-                              num_pages, nh, window, scale, nsplit, part_o, part_ml, err):
+                              num_pages, nh, window, scale, nsplit, part_o, part_ml, err,
+                              plan: Optional[torch.Tensor] = None):
     """Decode attention that finishes the qkv projection itself: ``parts [ks, T, (nh + 2 nkv) * hd]`` are the
     projection's float32 partial sums, ``bias`` its bias or None, ``table [T, hd / 2, 2]`` the step's cos/sin.
     Every CTA adds, biases and rotates the query rows it needs; the CTA that holds a token's own position
@@ -620,7 +625,8 @@ def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache
                                                  _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                                  _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                                  int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                                 int(nsplit), _ptr(err), _stream()), "attention_decode_qkv_bf16")
+                                                 int(nsplit), _ptr(plan), _ptr(err), _stream()),
+           "attention_decode_qkv_bf16")
     if nsplit > 1:
         global launch_count
         launch_count += 1          # the merge kernel
@@ -744,6 +750,112 @@ def attention_bf16_supported(hd: int, nh: int, nkv: int) -> bool:
     return bool(lib().prism_attention_bf16_supported(hd, nh, nkv))
 
 
+def decode_tiles(position: int, window: Optional[int]) -> int:
+    """64-key tiles the token at ``position`` sees (its own key included)."""
+    lo = max(0, position - window + 1) if window else 0
+    return position // 64 - lo // 64 + 1
+
+
+def decode_used_splits(tiles: int, target_x16: int, cap: int) -> int:
+    """CTAs that share one request's keys under a plan: as many as keep each at or below the target, none with
+    fewer than ``DECODE_MIN_TILES`` tiles, at most ``cap`` (csrc/attention_bf16.cuh computes the same)."""
+    target = max(target_x16, DECODE_MIN_TILES * 16)              # a descriptor without a plan holds 0
+    return min(max(min(-(-tiles * 16 // target), tiles // DECODE_MIN_TILES), 1), cap)
+
+
+# Where one wave of CTAs leaves the average CTA below this fraction of the longest one (many requests too short
+# to be split hold a place each and leave it early), the plan goes to CTAs of about half the size in two waves:
+# the second wave moves into the places the short CTAs have left.  Equal contexts never qualify (all CTAs are the
+# longest), and there two waves lose: batch 48 at 2,100 keys 4.19 -> 4.28 ms a step, batch 56 4.40 -> 4.64 ms.
+DECODE_SECOND_WAVE_BELOW = 0.75
+
+
+def _tiles_of(positions, window: Optional[int]):
+    pos = np.asarray(positions, dtype=np.int64)
+    lo = np.maximum(pos - window + 1, 0) if window else 0
+    return pos // 64 - lo // 64 + 1
+
+
+def _used_splits(tiles, target_x16: int, cap: int = 64):
+    """``decode_used_splits`` for an array of requests."""
+    target = max(target_x16, DECODE_MIN_TILES * 16)
+    used = np.minimum((tiles * 16 + (target - 1)) // target, np.minimum(tiles // DECODE_MIN_TILES, cap))
+    return np.maximum(used, 1, out=used)
+
+
+def _smallest_target(tiles, nkv: int, places: int) -> int:
+    """The smallest target (tiles per CTA, in sixteenths), from the tiles divided by the places on, with which
+    the requests' CTAs fit into ``places``.  It is seldom much more than that: the search widens from there."""
+    tiles16, most = tiles * 16, np.minimum(tiles // DECODE_MIN_TILES, 64)
+
+    def fits(target):
+        used = np.minimum((tiles16 + (target - 1)) // target, most)
+        return (int(used.sum()) + int(np.count_nonzero(used == 0))) * nkv <= places
+    lo = max(DECODE_MIN_TILES * 16, -(-int(tiles.sum()) * nkv * 16 // places))
+    if fits(lo):
+        return lo
+    top = max(lo, int(tiles.max()) * 16)                      # one CTA each: fits, or nothing does
+    step = max(1, lo // 8)
+    hi = min(top, lo + step)
+    while hi < top and not fits(hi):
+        lo, step = hi, step * 2
+        hi = min(top, lo + step)
+    lo += 1                                                   # lo does not fit, hi does
+    while lo < hi:
+        mid = (lo + hi) // 2
+        if fits(mid):
+            hi = mid
+        else:
+            lo = mid + 1
+    return lo
+
+
+def decode_split_target(positions, nkv: int, window: Optional[int], sms: Optional[int] = None) -> int:
+    """The decode kernel's plan for a step: 64-key tiles per CTA, in sixteenths - the smallest target with which
+    the CTAs of the step's decoding requests (``decode_used_splits`` for each, times the kv heads) still fit on
+    the GPU at once, two per SM.  A long context among short ones is then shared among many CTAs while the short
+    ones take one each, and no CTA runs much longer than the rest.  For equal contexts this is the rule measured
+    before: 11 CTAs per (token, kv head) at batch 1 and 2,100 keys, 9 at batch 8, 4 at batch 16, 1 from batch 48
+    on.  Where many short requests hold most of the places, so that the average CTA is far shorter than the
+    longest (``DECODE_SECOND_WAVE_BELOW``), the target is the one that fits into twice the places: the short
+    CTAs end early and the second wave takes their places (64 requests of 128 to 4,096 keys, 4 kv heads: 5.31 ->
+    4.93 ms a step; 32 requests, 8 kv heads: 9.28 -> 8.74 ms; 8 requests, whose CTAs are all about as long:
+    3.03 -> 3.16 ms, which is why it is no general rule).  A batch so large that one CTA per (token, kv head) is
+    more than fits at once: the same, from the waves that this takes."""
+    slots = 2 * (sms or num_sms())
+    tiles = _tiles_of(positions, window)
+    places = slots * max(1, -(-len(tiles) * nkv // slots))       # the waves that one CTA each needs in any case
+    target = _smallest_target(tiles, nkv, places)
+    used = _used_splits(tiles, target)
+    if tiles.sum() / used.sum() < DECODE_SECOND_WAVE_BELOW * (tiles / used).max():
+        target = _smallest_target(tiles, nkv, places + slots)
+    return target
+
+
+def decode_plan_for(positions, nkv: int, window: Optional[int], sms: Optional[int] = None):
+    """``(target_x16, cap)`` for a step's decoding requests: the plan and the most CTAs any request gets under
+    it.  A large batch whose long, equal contexts leave one CTA per (token, kv head) and the GPU unevenly
+    filled (256 CTAs are two on 108 SMs and one on 40) gets the few equal splits that even it out
+    (``DECODE_BALANCE_FROM_TILES``; batch 64 at 32,768 keys: 717 -> 673 us)."""
+    n_sms = sms or num_sms()
+    target = decode_split_target(positions, nkv, window, n_sms)
+    tiles = _tiles_of(positions, window)
+    cap = int(_used_splits(tiles, target).max())
+    least = int(tiles.min())
+    if cap == 1 and least >= DECODE_BALANCE_FROM_TILES:
+        def fill(k):
+            m = len(tiles) * nkv * k / n_sms
+            return m / -(-m // 1)
+        for k in range(2, 9):
+            if least // k < 16:
+                break
+            if fill(k) >= 0.95 > fill(1):
+                target = max(DECODE_MIN_TILES * 16, -(-least * 16 // k))
+                cap = int(_used_splits(tiles, target).max())
+                break
+    return target, cap
+
+
 DECODE_MIN_TILES = 3                # 64-key tiles a split CTA keeps at least (csrc/attention_bf16.cuh: DEC_MIN_TILES)
 DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what the balance gains (batch 64: 8,192 keys
                                     # 203 -> 201 us in 4 splits, 32,768 keys 717 -> 673 us)
@@ -820,6 +932,16 @@ def _attention_portions(ctx, q, out, cache, window, scale, first_seg: int):
                                window, scale, ctx.err)
 
 
+def _decode_grid(ctx, cache, nd: int, nkv: int, window: Optional[int]):
+    """``(CTAs per (token, kv head), plan)`` for the decode kernel.  A step whose descriptor carries a plan for
+    this cache group (the runner computes one from the requests' real contexts) gets it and the grid extent
+    that goes with it; otherwise the splits are equal for all requests and chosen from the longest context."""
+    cap = getattr(ctx, "split_caps", {}).get(getattr(cache, "group", None))
+    if cap:
+        return cap, (ctx.decode_plan[cache.group] if cap > 1 else None)      # one CTA each: nothing to plan
+    return decode_splits(nd, nkv, ctx.max_kv_len, window, balance=ctx.host is not None), None
+
+
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[int], scale: float):
     """Attention of the step's tokens over one cache plane.  ``cache`` is a
     ``PagedCacheView``; the kernel is chosen by dtype and shape, and the
@@ -836,11 +958,12 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
             if not decoders_apart(nd, longest, window):
                 nd = 0
         if nd > 0:
-            nsplit = decode_splits(nd, nkv, ctx.max_kv_len, window, balance=ctx.host is not None)
+            nsplit, plan = _decode_grid(ctx, cache, nd, nkv, window)
             part_o = ctx.alloc((nd, nh, nsplit, hd), torch.float32)
             part_ml = ctx.alloc((nd, nh, nsplit, 2), torch.float32)
             attention_decode_bf16(q[:nd], out[:nd], cache.k, cache.v, cache.block_table, ctx.positions[:nd],
-                                  ctx.tok_seg[:nd], cache.num_pages, window, scale, nsplit, part_o, part_ml, ctx.err)
+                                  ctx.tok_seg[:nd], cache.num_pages, window, scale, nsplit, part_o, part_ml, ctx.err,
+                                  plan=plan)
         if nd < ctx.S:
             _attention_portions(ctx, q, out, cache, window, scale, nd)
         return
@@ -877,12 +1000,12 @@ def qkv_attention(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[tor
                 rope_table(ctx.positions, rot.inv_freq, table)
             parts = ctx.alloc((ks, T, (nh + 2 * nkv) * hd), torch.float32)
             gemm_tc(x, qkv_w, None, parts, EPI_PARTIAL, ksplit=ks)
-            nsplit = decode_splits(T, nkv, ctx.max_kv_len, window, balance=ctx.host is not None)
+            nsplit, plan = _decode_grid(ctx, cache, T, nkv, window)
             part_o = ctx.alloc((T, nh, nsplit, hd), torch.float32)
             part_ml = ctx.alloc((T, nh, nsplit, 2), torch.float32)
             attention_decode_qkv_bf16(parts, qkv_b, table, ctx.max_positions, out, cache.k, cache.v, cache.block_table,
                                       ctx.positions, ctx.tok_seg, cache.num_pages, nh, window, scale, nsplit,
-                                      part_o, part_ml, ctx.err)
+                                      part_o, part_ml, ctx.err, plan=plan)
             return
     q = qkv_rotate_store(ctx, x, qkv_w, qkv_b, nh, nkv, hd, rot, cache)
     attention(ctx, q, out, cache, window, scale)

@@ -185,6 +185,52 @@ def test_thirteen_decoding_requests_beside_a_prompt_portion(folder_and_plain, mo
             assert err <= ref.bound16[rid], (rid, pos, err, scale, ref.bound16[rid])
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_requests_of_unequal_length_decode_together(folder_and_plain, graphs, monkeypatch):
+    """Four requests of 1,500, 40, 600 and 130 tokens decode their last tokens in the same steps.  The step's
+    descriptor carries the decode kernel's plan: the long request is shared among several CTAs per kv head, the
+    short ones take one each.  Every logit row against the plain model."""
+    from prism_b200 import ops
+    from prism_b200.engine.runner import ModelRunner
+    from prism_b200.weights.loader import load_model_folder
+    folder, _, _ = folder_and_plain
+    seen = []
+    real = ops.attention_decode_bf16
+
+    def spy(q, out, k, v, bt, pos, seg, npg, window, scale, nsplit, po, pml, err, plan=None):
+        seen.append((q.shape[0], window, nsplit, None if plan is None else int(plan.item()) if not graphs else -1))
+        return real(q, out, k, v, bt, pos, seg, npg, window, scale, nsplit, po, pml, err, plan=plan)
+    monkeypatch.setattr(ops, "attention_decode_bf16", spy)
+    cfg, t = P.load_folder(folder, device="cuda:0")
+    seqs = {"long": random_tokens(8192, 1500, 31), "tiny": random_tokens(8192, 40, 32),
+            "mid": random_tokens(8192, 600, 33), "short": random_tokens(8192, 130, 34)}
+    with torch.no_grad():
+        ref = RefLogits(cfg, t, seqs, {k: P.forward(cfg, t, v) for k, v in seqs.items()})
+        for k in seqs:
+            ref[k] = ref[k].cpu()
+    tail, steps = 6, []
+    for rid, seq in seqs.items():
+        steps.append(dict(step=len(steps), entries=[dict(id=rid, tokens=seq[:-tail], want=[len(seq) - tail - 1])], end=[]))
+    for j in range(tail):
+        steps.append(dict(step=len(steps), end=list(seqs) if j == tail - 1 else [],
+                          entries=[dict(id=rid, tokens=[seq[len(seq) - tail + j]], want=[0]) for rid, seq in seqs.items()]))
+    _, model, pool = load_model_folder(folder, "cuda:0", torch.bfloat16)
+    runner = ModelRunner(model, "cuda:0", torch.bfloat16, 64, trace_budget(steps, 64) // 64, 4, max_seq_len=2048,
+                         use_cuda_graph=graphs, graph_batch_sizes=(1, 4))
+    got = run_trace(runner, steps)
+    full = [s for s in seen if s[0] == 4 and s[1] is None]       # the layers that keep every key
+    assert full and all(ns == 8 and plan is not None for _, _, ns, plan in full), full[:4]
+    if not graphs:
+        want = ops.decode_split_target([1494, 34, 594, 124], 4, None)
+        assert full[0][3] == want and [ops.decode_used_splits(ops.decode_tiles(p, None), want, 8)
+                                       for p in (1494, 34, 594, 124)] == [8, 1, 3, 1]
+    for rid, seq in seqs.items():
+        for pos in range(len(seq) - tail - 1, len(seq)):
+            err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())
+            assert err <= ref.bound16[rid], (rid, pos, err, ref.bound16[rid])
+    assert runner.cache.pages_in_use() == 0
+
+
 def test_generation_with_prompts_prefilled_in_portions(folder_and_plain):
     """``Engine.generate`` with ``prefill_chunk`` shorter than the prompts and a token budget that makes
     portions share steps with decoding requests, at these layer sizes, CUDA graphs and pipelined decoding on:

@@ -14,7 +14,8 @@ def test_layout_offsets_are_aligned_and_disjoint():
             assert o % 4 == 0 and o + n <= o2                  # 4 int32 = 16 bytes; no overlap
         assert spans[-1][0] + spans[-1][1] <= lay.total
         assert set(lay.off) == {"token_ids", "positions", "tok_seg", "seg_start", "cached_len", "q_len",
-                                "state_slots", "logit_rows"} | {f"bt{g}" for g in groups}
+                                "state_slots", "logit_rows", "decode_plan"} | {f"bt{g}" for g in groups}
+        assert lay.off["decode_plan"][1] == len(groups)
 
 
 def test_pack_and_views():
@@ -32,6 +33,11 @@ def test_pack_and_views():
     assert ctx.state_slots.tolist() == [2, 0] and ctx.logit_rows.tolist() == [0, 3]
     assert ctx.block_tables[0].tolist() == [[5, 2, 7, 40], [3, 1, 40, 40]]
     assert ctx.block_tables[1].tolist() == [[41, 41, 6, 41], [0, 41, 41, 41]]
+    assert ctx.decode_plan[0].tolist() == [0] and ctx.decode_plan[1].tolist() == [0] and ctx.split_caps == {}
+    planned = pack_batch(lay, tok, pos, seg_of, [0, 1, 4], [9, 4], [1, 3], [2, 0], [0, 3], rows, {0: 40, 1: 41},
+                         decode_plan={1: 77})
+    ctx2 = StepContext(lay, planned, torch.float32, "cpu", None, 64, None, 3, 10)
+    assert ctx2.decode_plan[0].tolist() == [0] and ctx2.decode_plan[1].tolist() == [77]
     # a pure decode step is recognised by its longest segment
     assert StepContext(lay, host, torch.float32, "cpu", None, 64, None, 1, 10).decode_only
 

@@ -1,6 +1,8 @@
 """How many CTAs share the keys of a query tile (prefill) or of a (token, kv head) (decode): the
 host-side choices of ``prism_b200.ops``, which need no GPU."""
 
+import random
+
 import pytest
 
 from prism_b200 import ops
@@ -71,3 +73,49 @@ def test_decoders_leave_a_mixed_step_for_the_decode_kernel():
     assert ops.decoders_apart(ops.MIXED_SPLIT_MIN, 100, None)
     assert ops.decoders_apart(1, 6001, None)                         # one long context is enough
     assert not ops.decoders_apart(1, 6001, 512)
+
+
+def test_decode_plan_reproduces_the_measured_choices_for_equal_contexts():
+    """Equal contexts of 2,100 keys on 148 SMs with 4 kv heads: the plan gives every request the number of CTAs
+    that was measured best for its batch size."""
+    for batch, want in [(1, 11), (8, 9), (16, 4), (24, 3), (32, 2), (40, 1), (48, 1), (56, 1), (64, 1)]:
+        target, cap = ops.decode_plan_for([2099] * batch, 4, None, sms=148)
+        assert cap == want, (batch, cap)
+        assert ops.decode_used_splits(ops.decode_tiles(2099, None), target, 64) == want
+    # the few equal splits that even out a large batch against long contexts
+    target, cap = ops.decode_plan_for([32767] * 64, 4, None, sms=148)
+    assert cap == ops.decode_splits(64, 4, 32768, None, sms=148) > 1
+
+
+def test_decode_plan_shares_a_ragged_batch_by_context():
+    """One long context among short ones: the long one gets CTAs in proportion, the short ones a single CTA,
+    all CTAs together fit in one wave, and no CTA gets fewer than the least number of tiles."""
+    sms = 148
+    rng = random.Random(3)
+    for _ in range(200):
+        batch = rng.choice([1, 2, 5, 8, 17, 32, 64])
+        nkv = rng.choice([1, 2, 4, 8])
+        window = rng.choice([None, None, 300, 4096])
+        pos = [rng.choice([0, 5, 63, 64, 700, 5000, 40000]) + rng.randrange(64) for _ in range(batch)]
+        target, cap = ops.decode_plan_for(pos, nkv, window, sms=sms)
+        used = [ops.decode_used_splits(ops.decode_tiles(p, window), target, cap) for p in pos]
+        assert max(used) == cap >= 1
+        if batch * nkv <= 2 * sms:                    # one CTA each fits at once: then the plan fills one wave,
+            n = sum(used) * nkv                       # or two where many CTAs are short and end early
+            assert n <= 2 * sms or (n <= 4 * sms and sum(ops.decode_tiles(p, window) for p in pos) / sum(used)
+                                    < 0.75 * max(ops.decode_tiles(p, window) / u for p, u in zip(pos, used)) * 2)
+        for p, u in zip(pos, used):
+            t = ops.decode_tiles(p, window)
+            assert u == 1 or t // u >= ops.DECODE_MIN_TILES
+    # 64 requests of 128 to 4,096 keys: one wave would leave CTAs of 2 to 58 tiles; two waves of at most 21
+    rng = random.Random(0)
+    ragged = [4096] + [rng.randint(128, 4096) for _ in range(63)]
+    target, cap = ops.decode_plan_for(ragged, 4, None, sms=sms)
+    used = [ops.decode_used_splits(ops.decode_tiles(p, None), target, cap) for p in ragged]
+    assert 2 * sms < sum(used) * 4 <= 4 * sms and max(ops.decode_tiles(p, None) / u for p, u in zip(ragged, used)) < 22
+    target, cap = ops.decode_plan_for([16383] + [499] * 31, 4, None, sms=sms)
+    assert cap > 16 and ops.decode_used_splits(ops.decode_tiles(499, None), target, cap) == 1
+    # a window bounds what a token sees
+    assert ops.decode_tiles(40000, 128) <= 3 and ops.decode_tiles(10, 128) == 1 and ops.decode_tiles(64, None) == 2
+    # a descriptor without a plan holds 0: the least number of tiles per CTA decides
+    assert ops.decode_used_splits(33, 0, 64) == 11 and ops.decode_used_splits(33, 0, 4) == 4

@@ -519,6 +519,57 @@ def test_attention_decode_bf16(case):
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
+@pytest.mark.parametrize("case", DECODE_CASES)
+@pytest.mark.parametrize("target_x16", [0, 48, 52, 130, 1000, 1 << 20])
+def test_attention_decode_bf16_under_a_plan(case, target_x16):
+    """With a plan (tiles per CTA, in sixteenths) every request is shared among the CTAs its own length asks
+    for, at most the grid's extent; the partials beyond hold NaN and must not be read.  The host's
+    ``decode_used_splits`` says how many there are."""
+    ops = _ops()
+    nh, nkv, hd, P, window, ctxs, cap = case
+    c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=22)
+    out = torch.full((c.T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    part_o = torch.full((c.T, nh, cap, hd), float("nan"), device=DEV)
+    part_ml = torch.full((c.T, nh, cap, 2), float("nan"), device=DEV)
+    err, scale = _err(), hd ** -0.5
+    plan = torch.tensor([target_x16], dtype=torch.int32, device=DEV)
+    ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
+    ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
+                              cap, part_o, part_ml, err, plan=plan)
+    assert int(err) == 0 and not torch.isnan(out.float()).any()
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+    for t, n in enumerate(ctxs if cap > 1 else []):    # exactly the planned partials were written (one CTA: none)
+        used = ops.decode_used_splits(ops.decode_tiles(n, window), target_x16, cap)
+        written = (~torch.isnan(part_ml[t, 0, :, 0])).sum().item()
+        assert written == used, (t, n, written, used)
+
+
+def test_attention_decode_qkv_under_a_plan():
+    """The decode kernel that finishes the projection takes the same plan."""
+    ops = _ops()
+    nh, nkv, hd, P, window, ctxs, cap = 12, 2, 128, 64, None, [1300, 64, 200, 0, 5000], 16
+    c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=23)
+    T, ks, D = c.T, 2, (nh + 2 * nkv) * hd
+    parts = _rand((ks, T, D), torch.float32, 62, scale=0.5)
+    inv = (1.0 / (1e4 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).to(DEV)
+    table = torch.empty(T, hd // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(c.positions, inv, table)
+    scale, err = hd ** -0.5, _err()
+    outs = []
+    for plan in (None, torch.tensor([ops.decode_split_target(ctxs, nkv, window, sms=20)], dtype=torch.int32, device=DEV)):
+        k, v = c.k.clone(), c.v.clone()
+        got = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        po = torch.full((T, nh, cap, hd), float("nan"), device=DEV)
+        pml = torch.full((T, nh, cap, 2), float("nan"), device=DEV)
+        ops.attention_decode_qkv_bf16(parts, None, table, 1 << 20, got, k, v, c.bt, c.positions, c.tok_seg, c.num_pages,
+                                      nh, window, scale, cap, po, pml, err, plan=plan)
+        assert int(err) == 0 and not torch.isnan(got.float()).any()
+        outs.append(got.float())
+        if plan is not None:
+            assert sorted((~torch.isnan(pml[:, 0, :, 0])).sum(1).tolist()) != [cap] * T      # the plan was followed
+    assert torch.allclose(outs[0], outs[1], atol=4e-3, rtol=1e-2)
+
+
 @pytest.mark.parametrize("case", DECODE_CASES + [(8, 2, 64, 16, 40, [100, 39, 40, 41, 0], 3)])     # head sizes 16 .. 128
 @pytest.mark.parametrize("bias_dtype", [None, torch.bfloat16, torch.float32])
 def test_attention_decode_finishes_the_qkv_projection(case, bias_dtype):
