@@ -99,6 +99,31 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two float32 in one 64-bit register and the packed arithmetic of sm_100 on them: one instruction where the
+// softmax would otherwise issue two (its warps are short of issue slots, not of arithmetic throughput).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -303,7 +328,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
+            for (int i = 0; i < 32; ++i) mx = max3(mx, __uint_as_float(sa[i]), __uint_as_float(sb[i]));
             // The exponent's reference m_run follows the row maximum lazily: it moves only when the
             // maximum has grown by more than 2^RESCALE_STEP, so that O seldom has to be rescaled.  Until
             // then the probabilities are at most 2^RESCALE_STEP instead of 1, which float32 sums and bf16
@@ -313,18 +338,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float m_new = move ? m_tile : m_run;
             const float mu = m_new == -INFINITY ? 0.f : m_new;
             const float corr = move ? ex2(m_run - mu) : 1.f;           // 0 for a row that saw nothing yet
-            float lsum = 0.f;
             uint32_t pr[32];
+            const uint64_t scale2 = f2_pack(scale_log2, scale_log2), neg_mu2 = f2_pack(-mu, -mu);
+            uint64_t sum_a = f2_pack(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float p0 = ex2(fmaf(__uint_as_float(sa[2 * i]), scale_log2, -mu));
-                const float p1 = ex2(fmaf(__uint_as_float(sa[2 * i + 1]), scale_log2, -mu));
-                const float p2 = ex2(fmaf(__uint_as_float(sb[2 * i]), scale_log2, -mu));
-                const float p3 = ex2(fmaf(__uint_as_float(sb[2 * i + 1]), scale_log2, -mu));
-                lsum += (p0 + p1) + (p2 + p3);
+                float p0, p1, p2, p3;
+                f2_unpack(f2_fma(f2_pack(__uint_as_float(sa[2 * i]), __uint_as_float(sa[2 * i + 1])), scale2, neg_mu2), p0, p1);
+                f2_unpack(f2_fma(f2_pack(__uint_as_float(sb[2 * i]), __uint_as_float(sb[2 * i + 1])), scale2, neg_mu2), p2, p3);
+                p0 = ex2(p0), p1 = ex2(p1), p2 = ex2(p2), p3 = ex2(p3);
+                sum_a = f2_add(sum_a, f2_pack(p0, p1));
+                sum_b = f2_add(sum_b, f2_pack(p2, p3));
                 pr[i] = pack2(p0, p1);
                 pr[16 + i] = pack2(p2, p3);
             }
+            float l0, l1;
+            f2_unpack(f2_add(sum_a, sum_b), l0, l1);
+            const float lsum = l0 + l1;
             l_run = l_run * corr + lsum;
             m_run = m_new;
             // O holds the sum up to tile j-1 relative to the old maximum: rescale this row when it moved
