@@ -5,8 +5,8 @@ through the engine's own step function (CUDA graphs on), random weights:
                                                   them 4,096), then 64 equal contexts of their mean
 
 Prints one JSON line for each: milliseconds a step over 100 steps after 10 warm-ups (CUDA events).  With
-``--no-plan`` the step's descriptor carries no plan for the decode attention kernel, and every request gets the
-same number of CTAs, chosen from the longest context (the behaviour the plan replaced).
+``--no-plan`` the step's descriptor carries no work items for the decode attention kernel, and every request gets
+the same number of CTAs, chosen from the longest context (the behaviour the items replaced).
 """
 
 import argparse
@@ -41,7 +41,7 @@ def main():
     eng = Engine(None, ec, dtype="bfloat16", config=cfg, random_seed=0)
     runner = eng.runner
     if args.no_plan:
-        runner._decode_plan = lambda cached, qlen: ({}, {})
+        runner._decode_work = lambda cached, qlen, n_real=None: {}
     g = torch.Generator().manual_seed(1)
     out = torch.empty(B, dtype=torch.int32, device="cuda:0")
     for name, lens in (("equal", uniform), ("unequal", ragged)):

@@ -24,21 +24,25 @@ PRISM_EXPORT int prism_attention_bf16_supported(int hd, int nh, int nkv) {
 
 // Decode: T tokens, one per request.  part_o: float [T, nh, nsplit, hd]; part_ml: float [T, nh, nsplit, 2].
 // With nsplit > 1 a second kernel merges the splits' partial results.
-// plan (optional, device): one int, the step's tiles per CTA in sixteenths (ops.decode_split_target): a token's keys
-// are then shared among decode_used_splits(its tiles, plan[0], nsplit) CTAs instead of nsplit, and the rest of the
-// grid's CTAs return at once.
+// items (optional, device, 16-byte aligned): n_items work items {token, split | used << 16, position, segment} and
+// starts [T] (token t's items are the `used` ones from `first` on, starts[t] = first | used << 16; at most 65,535
+// items): every token's keys are then shared among the
+// CTAs the host chose for it (ops.decode_work_items); nsplit is the most items of a token, part_o is
+// float [n_items, nh, hd] and part_ml float [n_items, nh, 2], positions and tok_seg are not read.
 PRISM_EXPORT int prism_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
                                              const void* kc, const void* vc, const int* block_table,
                                              int bt_width, const int* positions, const int* tok_seg,
                                              int T, int nh, int nkv, int hd, int page_size, int num_pages,
                                              int window, float scale, float* part_o, float* part_ml,
-                                             int nsplit, const int* plan, int* err, cudaStream_t stream) {
+                                             int nsplit, const int* items, const int* starts, int n_items,
+                                             int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535)
+    if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535 ||
+        (items != nullptr && (starts == nullptr || n_items < 1 || n_items > 65535 || ((uintptr_t)items & 15))))
         return (int)cudaErrorInvalidValue;
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
-             window, scale, part_o, part_ml, nsplit, err, stream, nullptr, plan
+             window, scale, part_o, part_ml, nsplit, err, stream, nullptr, items, starts, n_items
 #define CALL(HD) prism::launch_decode<HD>(ARGS)
     PRISM_BY_HEAD_SIZE(hd, CALL);
 #undef CALL
@@ -54,9 +58,11 @@ PRISM_EXPORT int prism_attention_decode_qkv_bf16(const float* parts, int ks, con
                                                  void* vc, const int* block_table, int bt_width, const int* positions,
                                                  const int* tok_seg, int T, int nh, int nkv, int hd, int page_size,
                                                  int num_pages, int window, float scale, float* part_o, float* part_ml,
-                                                 int nsplit, const int* plan, int* err, cudaStream_t stream) {
+                                                 int nsplit, const int* items, const int* starts, int n_items,
+                                                 int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!prism_attention_bf16_supported(hd, nh, nkv) || nsplit < 1 || nkv > 65535 || T > 65535 || ks < 1 ||
+        (items != nullptr && (starts == nullptr || n_items < 1 || n_items > 65535 || ((uintptr_t)items & 15))) ||
         parts == nullptr || table == nullptr || ((uintptr_t)parts & 15) || ((uintptr_t)table & 15) ||
         ((uintptr_t)bias & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
         (bias_dtype != PRISM_DTYPE_F32 && bias_dtype != PRISM_DTYPE_BF16))
@@ -74,7 +80,7 @@ PRISM_EXPORT int prism_attention_decode_qkv_bf16(const float* parts, int ks, con
     f.max_pos = max_pos;
 #define ARGS (const __nv_bfloat16*)nullptr, 0, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc, \
              (const __nv_bfloat16*)vc, block_table, bt_width, positions, tok_seg, T, nh, nkv, page_size, num_pages, \
-             window, scale, part_o, part_ml, nsplit, err, stream, &f, plan
+             window, scale, part_o, part_ml, nsplit, err, stream, &f, items, starts, n_items
 #define CALL(HD) prism::launch_decode<HD>(ARGS)
     PRISM_BY_HEAD_SIZE(hd, CALL);
 #undef CALL
@@ -109,7 +115,7 @@ PRISM_EXPORT int prism_attention_merge_bf16(const float* part_o, const float* pa
     // one thread per output element: the block is the head size rounded up to whole warps
 #define CALL(HD) (int)prism::launch_kernel(prism::attn_merge_kernel<HD>, dim3(T * nh), dim3((HD + 31) / 32 * 32), 0, stream, \
                                            part_o, part_ml, nsplit, (__nv_bfloat16*)out, out_stride, nh,              \
-                                           (const int*)nullptr, (const int*)nullptr, 0)
+                                           (const int*)nullptr)
     PRISM_BY_HEAD_SIZE(hd, CALL);
 #undef CALL
 }

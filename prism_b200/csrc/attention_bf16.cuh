@@ -104,18 +104,15 @@ __device__ __forceinline__ void rotate4(const float (&x1)[4], const float (&x2)[
     hi = make_uint2(pack_bf16(y2[0], y2[1]), pack_bf16(y2[2], y2[3]));
 }
 
-// How many CTAs share the keys of one (token, kv head) when the step's descriptor carries a plan: the host
-// has looked for the smallest number of 64-key tiles per CTA (`target_x16`, in sixteenths) with which the CTAs
-// of all decoding requests together still fit on the GPU at once.  A request then gets as many CTAs as keep
-// each of them at or below the target - a long context many, a short one a single CTA - so that no CTA of a
-// ragged batch runs much longer than the others; never so many that one keeps fewer than DEC_MIN_TILES tiles,
-// at most `cap` (the grid's extent).  The same few integer operations run on the host (ops.decode_used_splits).
-__device__ __forceinline__ int decode_used_splits(int ntiles, int target_x16, int cap) {
-    const int target = max(target_x16, DEC_MIN_TILES * 16);                 // a descriptor without a plan holds 0
-    const int u = min((ntiles * 16 + target - 1) / target, ntiles / DEC_MIN_TILES);
-    return min(max(u, 1), cap);
-}
-
+// Work items.  With `items` the grid is flat: CTA (x = kv head, y = item) takes items[y] = {token, split | used << 16,
+// position, segment} - the host has shared every request's keys among `used` CTAs according to its own length
+// (ops.decode_work_items), so that a long context among short ones gets many CTAs and a short one a single CTA,
+// and no CTA of the step runs much longer than the others.  Items of one token are consecutive (the host may
+// put the tokens in any order, e.g. the longest CTAs first); item y leaves its partial result in slot y, and a
+// token with a single item writes its output itself.  token < 0: a place of the grid that this step does not use;
+// the host puts those last, and with the item as the grid's slow dimension they are launched after all others.
+// The items are part of the step's descriptor (complete before the step's first kernel); position and segment
+// travel with them so that the CTA's first load is all it needs to find its keys.
 template <int HD, bool FUSED = false>
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -125,7 +122,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                    int nkv, int page_size, int page_shift, int num_pages, int window, float scale_log2,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nsplit,
                    __nv_bfloat16* __restrict__ out, int out_stride, int* err, const DecodeQKV fq,
-                   const int* __restrict__ plan) {
+                   const int4* __restrict__ items) {
     __shared__ __align__(16) __nv_bfloat16 s_own_kv[FUSED ? 2 * HD : 8];     // FUSED: this step's own key and value
     constexpr int STRIDE = TileRow<HD>::STRIDE;
     constexpr int SUB_ELEMS = 16 * STRIDE;                           // one warp's 16 keys of a tile
@@ -133,35 +130,42 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][STRIDE]
     __nv_bfloat16* KV = Qs + 16 * STRIDE;                            // [warp][stage][K|V][16][STRIDE]
 
-    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = nh / nkv;
-    const int pos = positions[t];
-    const int* bt = block_table + (size_t)tok_seg[t] * bt_width;
+    int kvh, split, t, pos, seg, used = 0;
+    if (items != nullptr) {
+        const int4 it = items[blockIdx.y];
+        if (it.x < 0) return;
+        kvh = blockIdx.x, t = it.x, split = it.y & 0xffff, used = it.y >> 16, pos = it.z, seg = it.w;
+    } else {
+        split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+        pos = positions[t], seg = tok_seg[t];
+    }
+    const int* bt = block_table + (size_t)seg * bt_width;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int hi = pos;
     const int first_tile = lo / ATT_TILE, ntiles = hi / ATT_TILE - first_tile + 1;
-    // nsplit is chosen for the longest context the launch may meet (a captured graph knows a bound only): a
-    // shorter one is shared among fewer CTAs, DEC_MIN_TILES tiles each at least, and the rest leave empty partials
-    int per_split = max((ntiles + nsplit - 1) / nsplit, nsplit > 1 ? DEC_MIN_TILES : 1);
-    if (plan != nullptr) {
-        // the step's plan (part of its descriptor, complete before the step's first kernel): this request's
-        // share of the CTAs follows its own length; the CTAs beyond it have nothing to do and leave nothing
-        const int used = decode_used_splits(ntiles, plan[0], nsplit);
-        if (split >= used) return;
-        per_split = (ntiles + used - 1) / used;
-    }
+    // without items nsplit is chosen for the longest context the launch may meet: a shorter one is shared
+    // among fewer CTAs, DEC_MIN_TILES tiles each at least, and the rest leave empty partials
+    const int per_split = items != nullptr ? (ntiles + used - 1) / used
+                                           : max((ntiles + nsplit - 1) / nsplit, nsplit > 1 ? DEC_MIN_TILES : 1);
     const int t0 = first_tile + split * per_split;
     const int t1 = min(t0 + per_split, first_tile + ntiles);
+    const bool direct = items != nullptr ? used == 1 : nsplit == 1;      // the only split: no partial and no merge
 
-    float* po = part_o + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * HD;   // + row * nsplit * HD
-    float* pml = part_ml + (((size_t)t * nh + (size_t)kvh * g) * nsplit + split) * 2;
+    // partial results [token][head][split]: without items every token has nsplit slots per head, with items the
+    // token whose first item is f has its used * nh slots from slot f * nh on
+    const size_t head0 = (size_t)kvh * g;
+    const size_t prow = items != nullptr ? (size_t)used : (size_t)nsplit;      // slots between two heads' partials
+    const size_t pslot = (items != nullptr ? (size_t)(blockIdx.y - split) * nh : (size_t)t * nh * nsplit) + head0 * prow + split;
+    float* po = part_o + pslot * HD;        // + row * prow * HD
+    float* pml = part_ml + pslot * 2;       // + row * prow * 2
     if (t0 >= t1) {                       // nothing for this split: an empty partial
         pdl_wait();
-        for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * nsplit * HD + i % HD] = 0.f;
+        for (int i = tid; i < g * HD; i += ATT_THREADS) po[(size_t)(i / HD) * prow * HD + i % HD] = 0.f;
         for (int r = tid; r < g; r += ATT_THREADS) {
-            pml[(size_t)r * nsplit * 2] = -INFINITY;
-            pml[(size_t)r * nsplit * 2 + 1] = 0.f;
+            pml[(size_t)r * prow * 2] = -INFINITY;
+            pml[(size_t)r * prow * 2 + 1] = 0.f;
         }
         pdl_trigger_gemm();
         return;
@@ -401,14 +405,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             acc += red_o[((size_t)w * 16 + r) * HD + d] * f;
             L += red_l[w * 16 + r] * f;
         }
-        if (nsplit == 1) {
-            // the only split: this is the result, no partial and no merge
+        if (direct) {
             out[(size_t)t * out_stride + ((size_t)kvh * g + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc * (1.f / L) : 0.f);
         } else {
-            po[(size_t)r * nsplit * HD + d] = acc;
+            po[(size_t)r * prow * HD + d] = acc;
             if (d == 0) {
-                pml[(size_t)r * nsplit * 2] = M;
-                pml[(size_t)r * nsplit * 2 + 1] = L;
+                pml[(size_t)r * prow * 2] = M;
+                pml[(size_t)r * prow * 2 + 1] = L;
             }
         }
     }
@@ -422,54 +425,57 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 constexpr int MERGE_BATCH = 16;
 constexpr int MERGE_MAX_SPLITS = 256;      // weights kept in shared memory; more splits than this take the slow loop
 
-// `plan` (with `positions`, `window`): the decode kernel ran under a plan, only the first
-// decode_used_splits(...) partials of a token exist; `cap` is the partial arrays' extent.
+// `starts` (the decode kernel ran on work items): token t has `used` items from item `first` on, starts[t] =
+// first | used << 16, and its partials [head][split] lie from slot first * nh on; a token with one item has its
+// output already.  Without: [token][head][cap].
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   int cap, __nv_bfloat16* __restrict__ out, int out_stride, int nh,
-                                  const int* __restrict__ plan, const int* __restrict__ positions, int window) {
+                                  const int* __restrict__ starts) {
     __shared__ float s_w[MERGE_MAX_SPLITS];
     __shared__ float s_inv;
     pdl_trigger();
     const int t = blockIdx.x / nh, h = blockIdx.x % nh;
     int nsplit = cap;
-    if (plan != nullptr) {
-        const int pos = positions[t];
-        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        nsplit = decode_used_splits(pos / ATT_TILE - lo / ATT_TILE + 1, plan[0], cap);
+    size_t first = (size_t)blockIdx.x * cap;                    // slot of split 0
+    if (starts != nullptr) {
+        const int s0 = starts[t] & 0xffff;
+        nsplit = starts[t] >> 16;
+        if (nsplit <= 1) return;
+        first = (size_t)s0 * nh + (size_t)h * nsplit;
     }
     pdl_wait();
-    const float* po = pdl_fresh(part_o) + (size_t)blockIdx.x * cap * HD;          // the attention kernel's output
-    const float* pml = pdl_fresh(part_ml) + (size_t)blockIdx.x * cap * 2;
+    const float* po = pdl_fresh(part_o) + first * HD;          // the attention kernel's output
+    const float* pml = pdl_fresh(part_ml) + first * 2;
+    constexpr size_t ostep = HD, mstep = 2;
     // blockDim.x: HD rounded up to whole warps; a thread beyond HD (head sizes 16, 48, 80, 112) works on element
     // 0 again and stores nothing
     const bool mine = (int)threadIdx.x < HD;
     const int d = mine ? threadIdx.x : 0;
     if (nsplit > MERGE_MAX_SPLITS) {
         float M = -INFINITY;
-        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
+        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[mstep * s]);
         const float Mu = M == -INFINITY ? 0.f : M;
         float L = 0.f, acc = 0.f;
         for (int s = 0; s < nsplit; ++s) {
-            const float f = exp2_guard(pml[2 * s], Mu);
-            L += pml[2 * s + 1] * f;
-            acc += po[(size_t)s * HD + d] * f;
+            const float f = exp2_guard(pml[mstep * s], Mu);
+            L += pml[mstep * s + 1] * f;
+            acc += po[ostep * s + d] * f;
         }
         if (mine) out[(size_t)t * out_stride + h * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         return;
     }
     float v[MERGE_BATCH];
 #pragma unroll
-    for (int i = 0; i < MERGE_BATCH; ++i) v[i] = i < nsplit ? po[(size_t)i * HD + d] : 0.f;
+    for (int i = 0; i < MERGE_BATCH; ++i) v[i] = i < nsplit ? po[ostep * i + d] : 0.f;
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
-        const float2* ml = reinterpret_cast<const float2*>(pml);
         float2 mine[MERGE_MAX_SPLITS / 32];
         float M = -INFINITY;
 #pragma unroll
         for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
             const int s = lane + 32 * i;
-            mine[i] = s < nsplit ? ml[s] : make_float2(-INFINITY, 0.f);
+            mine[i] = s < nsplit ? *reinterpret_cast<const float2*>(pml + mstep * s) : make_float2(-INFINITY, 0.f);
             M = fmaxf(M, mine[i].x);
         }
 #pragma unroll
@@ -496,7 +502,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
         // splits that saw no key (a launch sized for a longer context) have weight 0: nothing is asked of them
 #pragma unroll
         for (int i = 0; i < MERGE_BATCH; ++i)
-            v[i] = (s0 + i < nsplit && s_w[s0 + i] != 0.f) ? po[(size_t)(s0 + i) * HD + d] : 0.f;
+            v[i] = (s0 + i < nsplit && s_w[s0 + i] != 0.f) ? po[ostep * (s0 + i) + d] : 0.f;
 #pragma unroll
         for (int i = 0; i < MERGE_BATCH; ++i)
             if (s0 + i < nsplit) acc += v[i] * s_w[s0 + i];
@@ -697,19 +703,21 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int 
                   const __nv_bfloat16* kc, const __nv_bfloat16* vc, const int* bt, int bt_width,
                   const int* positions, const int* tok_seg, int T, int nh, int nkv, int page_size,
                   int num_pages, int window, float scale, float* part_o, float* part_ml, int nsplit,
-                  int* err, cudaStream_t stream, const DecodeQKV* fused = nullptr, const int* plan = nullptr) {
+                  int* err, cudaStream_t stream, const DecodeQKV* fused = nullptr, const int* items = nullptr,
+                  const int* starts = nullptr, int n_items = 0) {
+    // with work items: a flat grid of n_items CTAs per kv head; nsplit is then the most items a token has
     static_assert(dec_smem<HD>() >= (size_t)(4 * 16 * HD + 128) * sizeof(float), "merge scratch must fit");
-    dim3 grid(nsplit, nkv, T);
+    dim3 grid(items != nullptr ? nkv : nsplit, items != nullptr ? n_items : nkv, items != nullptr ? 1 : T);
     auto kern = fused != nullptr ? attn_decode_kernel<HD, true> : attn_decode_kernel<HD, false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec_smem<HD>());
     cudaError_t rc = launch_kernel(kern, grid, dim3(ATT_THREADS), dec_smem<HD>(), stream, q, q_stride, kc, vc, bt, bt_width,
                                    positions, tok_seg, nh, nkv, page_size, page_shift_of(page_size), num_pages, window,
                                    scale * 1.4426950408889634f, part_o, part_ml, nsplit, out, out_stride, err,
-                                   fused != nullptr ? *fused : DecodeQKV(), plan);
+                                   fused != nullptr ? *fused : DecodeQKV(), reinterpret_cast<const int4*>(items));
     if (rc != cudaSuccess || nsplit == 1) return (int)rc;
     return (int)launch_kernel(attn_merge_kernel<HD>, dim3(T * nh), dim3((HD + 31) / 32 * 32), 0, stream,
-                              (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh, plan, positions,
-                              window);
+                              (const float*)part_o, (const float*)part_ml, nsplit, out, out_stride, nh,
+                              items != nullptr ? starts : (const int*)nullptr);
 }
 
 template <int HD>

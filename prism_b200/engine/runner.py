@@ -134,13 +134,14 @@ class ModelRunner:
         host_meta = dict(seg_start=seg_start, cached_len=cached, q_len=qlen, slots=slots, tok_seg=seg_of)
 
         S = len(segments)
-        plan, caps = self._decode_plan(cached, qlen)
         if self.use_cuda_graph and max_q == 1 and S <= self.graph_batch_sizes[-1]:
-            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows, token_source, plan, caps)
+            logits = self._step_graph(tok, pos, cached, slots, rows, block_rows, token_source)
         else:
-            layout = BatchLayout(len(tok), S, len(rows), self.cache.table_width, self.paged_groups)
+            work = self._decode_work(cached, qlen)
+            layout = BatchLayout(len(tok), S, len(rows), self.cache.table_width, self.paged_groups,
+                                 {g: len(w[0]) for g, w in work.items()})
             host = pack_batch(layout, tok, pos, seg_of, seg_start, cached, qlen, slots, rows,
-                              block_rows, self.pad_page, plan)
+                              block_rows, self.pad_page, work)
             dev = host.to(self.device, non_blocking=True)
             self.last_h2d_bytes = host.numel() * 4
             if token_source is not None:
@@ -148,29 +149,30 @@ class ModelRunner:
                 layout.view(dev, "token_ids").copy_(token_source[:S], non_blocking=True)
             ctx = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions,
                               host_meta, max_q, max_kv)
-            ctx.split_caps = caps
+            for g, w in work.items():                  # the host knows whether any request has more than one item
+                ctx.decode_work[g] = ctx.decode_work[g][:2] + (w[2], len(w[1]))
             views = self.storage.views(ctx.block_tables, ctx.state_slots, slots)
             logits = self.model.forward(ctx, views)
         for s in segments:
             self.cache.commit(s.req_id, len(s.tokens))
         return logits
 
-    def _decode_plan(self, cached, qlen):
-        """The decode attention kernel's plan for the single-token segments at the head of the batch, per
-        paged cache group: ``({group: tiles per CTA in sixteenths}, {group: most CTAs a request gets})``,
-        from the requests' own contexts, so that a long context among short ones is shared among many CTAs
-        (``ops.decode_plan_for``).  Empty when the batch starts with a prompt portion."""
+    def _decode_work(self, cached, qlen, n_real: Optional[int] = None) -> Dict[int, tuple]:
+        """The decode attention kernel's work items for the single-token segments at the head of the batch, per
+        paged cache group: ``{group: (items, starts, most items of a request)}`` from the requests' own contexts,
+        so that a long context among short ones is shared among many CTAs (``ops.decode_work_items``).  Empty
+        when the batch starts with a prompt portion.  ``n_real``: the segments after these are padding."""
         from .. import ops
         lead = 0
         while lead < len(qlen) and qlen[lead] == 1:
             lead += 1
         if not lead or os.environ.get("PRISM_DECODE_SPLITS", "0") != "0":
-            return {}, {}
-        plan, caps = {}, {}
+            return {}
+        work = {}
         for g in self.paged_groups:
             need = self.groups[g].need
-            plan[g], caps[g] = ops.decode_plan_for(cached[:lead], need.num_kv_heads, need.window, self._sms)
-        return plan, caps
+            work[g] = ops.decode_work_items(cached[:lead], need.num_kv_heads, need.window, self._sms, n_real)
+        return work
 
     # ---- decode graphs ---------------------------------------------------------------
     def _bucket(self, n: int) -> int:
@@ -179,36 +181,35 @@ class ModelRunner:
                 return b
         raise ValueError(n)
 
-    def _graph_caps(self, B: int, caps: Dict[int, int]) -> tuple:
-        """The grid extent of the decode attention kernel is part of a captured graph, so a bucket has one
-        graph per extent, and the extents are few: powers of two and the one that fills the GPU with B
-        requests (what a batch of equal, long contexts asks for).  The smallest that holds what the plan
-        wants; the kernel leaves the CTAs a request does not use empty."""
+    def _graph_places(self, items: Dict[int, int]) -> tuple:
+        """The decode attention kernel's grid is part of a captured graph: it has as many places for work items
+        as fill the GPU once (two CTAs per SM), twice, ... - the fewest that hold the step's items.  A bucket has
+        one graph for each number of waves that its steps have asked for, seldom more than two."""
         out = []
-        for g in self.paged_groups:
-            need = self.groups[g].need
-            fill = max(1, min(64, (2 * self._sms) // max(1, B * need.num_kv_heads)))
-            want = caps.get(g, fill)
-            out.append(min(c for c in sorted({1, 2, 4, 8, 16, 32, 64, fill}) if c >= min(want, 64)))
+        for g in self.paged_groups if items else ():
+            wave = max(1, 2 * self._sms // self.groups[g].need.num_kv_heads)
+            out.append(-(-max(1, items[g]) // wave) * wave)
         return tuple(out)
 
-    def _capture(self, B: int, caps: tuple) -> dict:
+    def _capture(self, B: int, places: tuple, merge: bool) -> dict:
         """Capture the decode step for a bucket of B one-token segments: static
-        descriptor buffer, every row's logits computed.  ``caps``: the decode attention
-        kernel's grid extent for each paged group (``_graph_caps``)."""
-        split_caps = dict(zip(self.paged_groups, caps))
-        layout = BatchLayout(B, B, B, self.cache.table_width, self.paged_groups)
+        descriptor buffer, every row's logits computed.  ``places``: the decode attention
+        kernel's places for work items in each paged group (``_graph_places``); ``merge``: whether
+        a request may have more than one item (else the graph has no merge kernels)."""
+        layout = BatchLayout(B, B, B, self.cache.table_width, self.paged_groups, dict(zip(self.paged_groups, places)))
         dev = torch.zeros(layout.total, dtype=torch.int32, device=self.device)
         pad_rows = {g: [[] for _ in range(B)] for g in self.paged_groups}
         host = pack_batch(layout, [0] * B, [0] * B, list(range(B)), list(range(B + 1)), [0] * B, [1] * B,
-                          [self.cache.max_seqs] * B, list(range(B)), pad_rows, self.pad_page)
+                          [self.cache.max_seqs] * B, list(range(B)), pad_rows, self.pad_page,
+                          self._decode_work([0] * B, [1] * B))
         dev.copy_(host)
         def fresh_ctx():
             # every run gets its own context: values parts keep for the length of a step (the
             # rotary table) must be produced inside the capture, in the graph's own memory
             c = StepContext(layout, dev, self.dtype, self.device, self.err, self.max_positions, None,
                             1, self.max_seq_len)
-            c.split_caps = split_caps
+            for g in c.decode_work:
+                c.decode_work[g] = c.decode_work[g][:2] + (2 if merge else 1, B)
             return c, self.storage.views(c.block_tables, c.state_slots, None)
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -226,10 +227,11 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         return dict(graph=graph, layout=layout, dev=dev, out=out, launches=ops.launch_count - before)
 
-    def _step_graph(self, tok, pos, cached, slots, rows, block_rows, token_source=None, plan=None, caps=None):
+    def _step_graph(self, tok, pos, cached, slots, rows, block_rows, token_source=None):
         S = len(tok)
         B = self._bucket(S)
-        key = (B, self._graph_caps(B, caps or {}))
+        work = self._decode_work(cached + [0] * (B - S), [1] * B, S)    # padded rows: one item each, at position 0
+        key = (B, self._graph_places({g: len(w[0]) for g, w in work.items()}), any(w[2] > 1 for w in work.values()))
         g = self._graphs.get(key)
         if g is None:
             g = self._graphs[key] = self._capture(*key)
@@ -238,7 +240,7 @@ class ModelRunner:
         br = {k: v + [[] for _ in range(pad)] for k, v in block_rows.items()}
         host = pack_batch(g["layout"], tok + [0] * pad, pos + [0] * pad, list(range(B)), list(range(B + 1)),
                           cached + [0] * pad, [1] * B, slots + [scratch_slot] * pad, list(range(B)),
-                          br, self.pad_page, plan)
+                          br, self.pad_page, work)
         g["dev"].copy_(host, non_blocking=True)
         self.last_h2d_bytes = host.numel() * 4
         if token_source is not None:
@@ -253,13 +255,19 @@ class ModelRunner:
         return out[torch.tensor(rows, device=self.device)]
 
     def warmup_graphs(self, sizes: Optional[Sequence[int]] = None) -> None:
-        """Capture the decode graphs ahead of time (executor.py:312-318): for every bucket the graph
-        that a batch of long contexts uses; those for short or ragged contexts follow at their first use."""
+        """Capture the decode graphs ahead of time (executor.py:312-318): for every bucket the two graphs
+        (with and without the merge of split contexts) whose decode attention grid fills the GPU once.  The
+        graphs with larger grids (many requests of very unequal length) follow at their first use."""
         if self.use_cuda_graph:
             for b in sizes or self.graph_batch_sizes:
-                key = (b, self._graph_caps(b, {}))
-                if key not in self._graphs and b <= self.graph_batch_sizes[-1]:
-                    self._graphs[key] = self._capture(*key)
+                if b > self.graph_batch_sizes[-1]:
+                    continue
+                work = self._decode_work([0] * b, [1] * b)
+                places = self._graph_places({g: len(w[0]) for g, w in work.items()})
+                for merge in ((True, False) if work else (False,)):
+                    key = (b, places, merge)
+                    if key not in self._graphs:
+                        self._graphs[key] = self._capture(*key)
 
     def invalidate_graphs(self) -> None:
         self._graphs.clear()

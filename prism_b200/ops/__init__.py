@@ -92,9 +92,9 @@ class _Sig:
                                _i, _f, _p, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
-                                   _p, _p, _i, _p, _p, _p]
+                                   _p, _p, _i, _p, _p, _i, _p, _p]
     prism_attention_decode_qkv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
-                                       _i, _f, _p, _p, _i, _p, _p, _p]
+                                       _i, _f, _p, _p, _i, _p, _p, _i, _p, _p]
     prism_attention_prefill_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i,
                                     _f, _p, _p]
     prism_attention_prefill_tc_supported = [_i, _i, _i, _i]
@@ -578,26 +578,39 @@ FORCE_GENERIC_ATTENTION = os.environ.get("PRISM_ATTENTION", "") == "generic"
 QKV_PARTIAL = os.environ.get("PRISM_QKV_PARTIAL", "1") != "0"
 
 
+def _check_decode_scratch(items, starts, T, nh, hd, nsplit, part_o, part_ml):
+    slots = T * nsplit                                   # partial results: one per (token, split) ...
+    if items is not None:                                # ... or one per work item
+        assert starts is not None and items.dtype == torch.int32 and starts.dtype == torch.int32
+        assert items.dim() == 2 and items.shape[1] == 4 and items.is_contiguous() and items.data_ptr() % 16 == 0
+        assert starts.numel() == T and starts.is_contiguous() and items.shape[0] <= 65535
+        slots = items.shape[0]
+    if nsplit > 1:
+        assert part_o.dtype == torch.float32 and part_o.numel() >= slots * nh * hd
+        assert part_ml.dtype == torch.float32 and part_ml.numel() >= slots * nh * 2
+
+
 def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_seg, num_pages, window,
-                          scale, nsplit, part_o, part_ml, err, plan: Optional[torch.Tensor] = None):
+                          scale, nsplit, part_o, part_ml, err, items: Optional[torch.Tensor] = None,
+                          starts: Optional[torch.Tensor] = None):
     """Tensor-core decode attention (one token per request) with the keys split
     over ``nsplit`` CTAs per (token, kv head); ``part_o [T, nh, nsplit, hd]`` and
     ``part_ml [T, nh, nsplit, 2]`` are float32 scratch for the partial results.
-    ``plan`` (device int32, one element: ``decode_split_target`` of the step): every
-    token's keys are then shared among ``decode_used_splits`` CTAs of its own, at most
-    ``nsplit``, and the rest of the grid returns at once."""
-    _cuda(q, out, k_cache, v_cache, block_table, positions, tok_seg, part_o, part_ml, plan)
+    With ``items`` (device int32 ``[n, 4]``) and ``starts`` (``[T]``), the step's work items
+    (``decode_work_items``), every token's keys are shared among the CTAs chosen for it; ``nsplit``
+    is then the most items of a token and the scratch ``[n, nh, hd]`` and ``[n, nh, 2]``."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, tok_seg, part_o, part_ml, items, starts)
     T, nh, hd = q.shape
     nkv, P = k_cache.shape[2], k_cache.shape[1]
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(2) == 1 and q.stride(1) == hd and out.stride(1) == 1
-    assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
-    assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
+    _check_decode_scratch(items, starts, T, nh, hd, nsplit, part_o, part_ml)
     _check(lib().prism_attention_decode_bf16(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache),
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                              _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                              int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                             int(nsplit), _ptr(plan), _ptr(err), _stream()), "attention_decode_bf16")
+                                             int(nsplit), _ptr(items), _ptr(starts), 0 if items is None else items.shape[0],
+                                             _ptr(err), _stream()), "attention_decode_bf16")
     if nsplit > 1:
         global launch_count
         launch_count += 1          # the merge kernel
@@ -605,7 +618,7 @@ def attention_decode_bf16(q, out, k_cache, v_cache, block_table, positions, tok_
 
 def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache, block_table, positions, tok_seg,
                               num_pages, nh, window, scale, nsplit, part_o, part_ml, err,
-                              plan: Optional[torch.Tensor] = None):
+                              items: Optional[torch.Tensor] = None, starts: Optional[torch.Tensor] = None):
     """Decode attention that finishes the qkv projection itself: ``parts [ks, T, (nh + 2 nkv) * hd]`` are the
     projection's float32 partial sums, ``bias`` its bias or None, ``table [T, hd / 2, 2]`` the step's cos/sin.
     Every CTA adds, biases and rotates the query rows it needs; the CTA that holds a token's own position
@@ -618,14 +631,15 @@ def attention_decode_qkv_bf16(parts, bias, table, max_pos, out, k_cache, v_cache
     assert table.dtype == torch.float32 and table.is_contiguous() and table.shape == (T, hd // 2, 2)
     assert k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (T, nh * hd)
-    assert part_o.dtype == torch.float32 and part_o.numel() >= T * nh * nsplit * hd
-    assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * nh * nsplit * 2
+    _cuda(items, starts)
+    _check_decode_scratch(items, starts, T, nh, hd, nsplit, part_o, part_ml)
     _check(lib().prism_attention_decode_qkv_bf16(_ptr(parts), ks, _ptr(bias), F32 if bias is None else _dt(bias),
                                                  _ptr(table), int(max_pos), _ptr(out), out.stride(0), _ptr(k_cache),
                                                  _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                                  _ptr(positions), _ptr(tok_seg), T, nh, nkv, hd, P, num_pages,
                                                  int(window or 0), float(scale), _ptr(part_o), _ptr(part_ml),
-                                                 int(nsplit), _ptr(plan), _ptr(err), _stream()),
+                                                 int(nsplit), _ptr(items), _ptr(starts),
+                                                 0 if items is None else items.shape[0], _ptr(err), _stream()),
            "attention_decode_qkv_bf16")
     if nsplit > 1:
         global launch_count
@@ -763,11 +777,12 @@ def decode_used_splits(tiles: int, target_x16: int, cap: int) -> int:
     return min(max(min(-(-tiles * 16 // target), tiles // DECODE_MIN_TILES), 1), cap)
 
 
-# Where one wave of CTAs leaves the average CTA below this fraction of the longest one (many requests too short
-# to be split hold a place each and leave it early), the plan goes to CTAs of about half the size in two waves:
-# the second wave moves into the places the short CTAs have left.  Equal contexts never qualify (all CTAs are the
-# longest), and there two waves lose: batch 48 at 2,100 keys 4.19 -> 4.28 ms a step, batch 56 4.40 -> 4.64 ms.
-DECODE_SECOND_WAVE_BELOW = 0.75
+# Where one wave leaves a quarter of the CTAs or more at less than half the longest CTA's length (many requests too
+# short to be split hold a place each and leave it early), the plan goes to CTAs of about half the size in two
+# waves: the second wave moves into the places the short CTAs have left.  Equal contexts never qualify (all CTAs are
+# the longest), and there two waves lose: batch 48 at 2,100 keys 4.19 -> 4.28 ms a step, batch 56 4.40 -> 4.64 ms.
+DECODE_SHORT_CTA = 0.5
+DECODE_SECOND_WAVE_FROM_SHARE = 0.25
 
 
 def _tiles_of(positions, window: Optional[int]):
@@ -810,35 +825,51 @@ def _smallest_target(tiles, nkv: int, places: int) -> int:
     return lo
 
 
-def decode_split_target(positions, nkv: int, window: Optional[int], sms: Optional[int] = None) -> int:
+# Splitting has to pay: where even the best plan leaves the longest CTA above this fraction of the longest request
+# (many requests of about the same length and only a few places to spare), every request keeps a single CTA and
+# the step needs no merge kernel (64 requests of 1,024 to 1,536 keys on 8 kv heads: ten of them could be halved,
+# the eleventh decides the kernel's time all the same).
+DECODE_SPLIT_GAIN = 0.75
+
+
+def decode_split_target(positions, nkv: int, window: Optional[int], sms: Optional[int] = None,
+                        n_real: Optional[int] = None) -> int:
     """The decode kernel's plan for a step: 64-key tiles per CTA, in sixteenths - the smallest target with which
     the CTAs of the step's decoding requests (``decode_used_splits`` for each, times the kv heads) still fit on
     the GPU at once, two per SM.  A long context among short ones is then shared among many CTAs while the short
     ones take one each, and no CTA runs much longer than the rest.  For equal contexts this is the rule measured
     before: 11 CTAs per (token, kv head) at batch 1 and 2,100 keys, 9 at batch 8, 4 at batch 16, 1 from batch 48
-    on.  Where many short requests hold most of the places, so that the average CTA is far shorter than the
-    longest (``DECODE_SECOND_WAVE_BELOW``), the target is the one that fits into twice the places: the short
+    on.  Where many short requests hold most of the places, so that many CTAs are far shorter than the
+    longest (``DECODE_SECOND_WAVE_FROM_SHARE``), the target is the one that fits into twice the places: the short
     CTAs end early and the second wave takes their places (64 requests of 128 to 4,096 keys, 4 kv heads: 5.31 ->
     4.93 ms a step; 32 requests, 8 kv heads: 9.28 -> 8.74 ms; 8 requests, whose CTAs are all about as long:
     3.03 -> 3.16 ms, which is why it is no general rule).  A batch so large that one CTA per (token, kv head) is
-    more than fits at once: the same, from the waves that this takes."""
+    more than fits at once: the same, from the waves that this takes.  ``n_real``: the requests after the first
+    ``n_real`` are padding (rows of a captured graph's bucket): they take a place each, but say nothing about
+    how unequal the step's CTAs are."""
     slots = 2 * (sms or num_sms())
     tiles = _tiles_of(positions, window)
+    real = slice(0, len(tiles) if n_real is None else n_real)
     places = slots * max(1, -(-len(tiles) * nkv // slots))       # the waves that one CTA each needs in any case
     target = _smallest_target(tiles, nkv, places)
     used = _used_splits(tiles, target)
-    if tiles.sum() / used.sum() < DECODE_SECOND_WAVE_BELOW * (tiles / used).max():
+    per = tiles[real] / used[real]
+    if used[real][per < DECODE_SHORT_CTA * per.max()].sum() >= DECODE_SECOND_WAVE_FROM_SHARE * used[real].sum():
         target = _smallest_target(tiles, nkv, places + slots)
+        used = _used_splits(tiles, target)
+    if (tiles / used).max() > DECODE_SPLIT_GAIN * tiles.max():
+        target = int(tiles.max()) * 16                           # one CTA each
     return target
 
 
-def decode_plan_for(positions, nkv: int, window: Optional[int], sms: Optional[int] = None):
+def decode_plan_for(positions, nkv: int, window: Optional[int], sms: Optional[int] = None,
+                    n_real: Optional[int] = None):
     """``(target_x16, cap)`` for a step's decoding requests: the plan and the most CTAs any request gets under
     it.  A large batch whose long, equal contexts leave one CTA per (token, kv head) and the GPU unevenly
     filled (256 CTAs are two on 108 SMs and one on 40) gets the few equal splits that even it out
     (``DECODE_BALANCE_FROM_TILES``; batch 64 at 32,768 keys: 717 -> 673 us)."""
     n_sms = sms or num_sms()
-    target = decode_split_target(positions, nkv, window, n_sms)
+    target = decode_split_target(positions, nkv, window, n_sms, n_real)
     tiles = _tiles_of(positions, window)
     cap = int(_used_splits(tiles, target).max())
     least = int(tiles.min())
@@ -854,6 +885,29 @@ def decode_plan_for(positions, nkv: int, window: Optional[int], sms: Optional[in
                 cap = int(_used_splits(tiles, target).max())
                 break
     return target, cap
+
+
+def decode_work_items(positions, nkv: int, window: Optional[int], sms: Optional[int] = None,
+                      n_real: Optional[int] = None):
+    """The decode attention kernel's work for a step: ``(items [n, 4], starts [B], most)`` as int32 arrays
+    and the most items any request has.  Request b (at ``positions[b]``, token and segment b of the step) gets
+    ``decode_plan_for``'s number of CTAs per kv head, less where fewer already leave each the same number of
+    tiles: ``used`` items ``{b, split | used << 16, position, b}`` from item ``first`` on, ``starts[b] = first |
+    used << 16``.  The requests whose CTAs are longest come first, so that when the items are more than fit on
+    the GPU at once the short ones run last.  ``n_real``: the requests after these are a graph bucket's padding."""
+    target, cap = decode_plan_for(positions, nkv, window, sms, n_real)
+    pos = np.asarray(positions, dtype=np.int64)
+    tiles = _tiles_of(pos, window)
+    used = _used_splits(tiles, target, cap)
+    per = -(-tiles // used)
+    used = -(-tiles // per)                                # no CTA without a tile
+    order = np.argsort(-per, kind="stable")
+    first = np.empty(len(pos), dtype=np.int64)
+    first[order] = np.cumsum(used[order]) - used[order]
+    tok = np.repeat(order, used[order])
+    split = np.arange(len(tok)) - first[tok]
+    items = np.stack([tok, split | (used[tok] << 16), pos[tok], tok], axis=1).astype(np.int32)
+    return items, (first | (used << 16)).astype(np.int32), int(used.max())
 
 
 DECODE_MIN_TILES = 3                # 64-key tiles a split CTA keeps at least (csrc/attention_bf16.cuh: DEC_MIN_TILES)
@@ -932,14 +986,17 @@ def _attention_portions(ctx, q, out, cache, window, scale, first_seg: int):
                                window, scale, ctx.err)
 
 
-def _decode_grid(ctx, cache, nd: int, nkv: int, window: Optional[int]):
-    """``(CTAs per (token, kv head), plan)`` for the decode kernel.  A step whose descriptor carries a plan for
-    this cache group (the runner computes one from the requests' real contexts) gets it and the grid extent
-    that goes with it; otherwise the splits are equal for all requests and chosen from the longest context."""
-    cap = getattr(ctx, "split_caps", {}).get(getattr(cache, "group", None))
-    if cap:
-        return cap, (ctx.decode_plan[cache.group] if cap > 1 else None)      # one CTA each: nothing to plan
-    return decode_splits(nd, nkv, ctx.max_kv_len, window, balance=ctx.host is not None), None
+def _decode_scratch(ctx, cache, nd: int, nh: int, nkv: int, hd: int, window: Optional[int]):
+    """``(nsplit, part_o, part_ml, items, starts)`` for the decode kernel.  A step whose descriptor carries work
+    items for this cache group (the runner makes them from the requests' real contexts) runs on them; otherwise
+    the splits are equal for all requests and chosen from the longest context."""
+    work = getattr(ctx, "decode_work", {}).get(getattr(cache, "group", None))
+    if work is not None and work[3] == nd:
+        items, starts, most = work[0], work[1][:nd], work[2]
+        n = items.shape[0]
+        return most, ctx.alloc((n, nh, hd), torch.float32), ctx.alloc((n, nh, 2), torch.float32), items, starts
+    nsplit = decode_splits(nd, nkv, ctx.max_kv_len, window, balance=ctx.host is not None)
+    return nsplit, ctx.alloc((nd, nh, nsplit, hd), torch.float32), ctx.alloc((nd, nh, nsplit, 2), torch.float32), None, None
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[int], scale: float):
@@ -958,12 +1015,10 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache, window: Optional[i
             if not decoders_apart(nd, longest, window):
                 nd = 0
         if nd > 0:
-            nsplit, plan = _decode_grid(ctx, cache, nd, nkv, window)
-            part_o = ctx.alloc((nd, nh, nsplit, hd), torch.float32)
-            part_ml = ctx.alloc((nd, nh, nsplit, 2), torch.float32)
+            nsplit, part_o, part_ml, items, starts = _decode_scratch(ctx, cache, nd, nh, nkv, hd, window)
             attention_decode_bf16(q[:nd], out[:nd], cache.k, cache.v, cache.block_table, ctx.positions[:nd],
                                   ctx.tok_seg[:nd], cache.num_pages, window, scale, nsplit, part_o, part_ml, ctx.err,
-                                  plan=plan)
+                                  items=items, starts=starts)
         if nd < ctx.S:
             _attention_portions(ctx, q, out, cache, window, scale, nd)
         return
@@ -1000,12 +1055,10 @@ def qkv_attention(ctx, x: torch.Tensor, qkv_w: torch.Tensor, qkv_b: Optional[tor
                 rope_table(ctx.positions, rot.inv_freq, table)
             parts = ctx.alloc((ks, T, (nh + 2 * nkv) * hd), torch.float32)
             gemm_tc(x, qkv_w, None, parts, EPI_PARTIAL, ksplit=ks)
-            nsplit, plan = _decode_grid(ctx, cache, T, nkv, window)
-            part_o = ctx.alloc((T, nh, nsplit, hd), torch.float32)
-            part_ml = ctx.alloc((T, nh, nsplit, 2), torch.float32)
+            nsplit, part_o, part_ml, items, starts = _decode_scratch(ctx, cache, T, nh, nkv, hd, window)
             attention_decode_qkv_bf16(parts, qkv_b, table, ctx.max_positions, out, cache.k, cache.v, cache.block_table,
                                       ctx.positions, ctx.tok_seg, cache.num_pages, nh, window, scale, nsplit,
-                                      part_o, part_ml, ctx.err, plan=plan)
+                                      part_o, part_ml, ctx.err, items=items, starts=starts)
             return
     q = qkv_rotate_store(ctx, x, qkv_w, qkv_b, nh, nkv, hd, rot, cache)
     attention(ctx, q, out, cache, window, scale)

@@ -188,8 +188,8 @@ def test_thirteen_decoding_requests_beside_a_prompt_portion(folder_and_plain, mo
 @pytest.mark.parametrize("graphs", [False, True])
 def test_requests_of_unequal_length_decode_together(folder_and_plain, graphs, monkeypatch):
     """Four requests of 1,500, 40, 600 and 130 tokens decode their last tokens in the same steps.  The step's
-    descriptor carries the decode kernel's plan: the long request is shared among several CTAs per kv head, the
-    short ones take one each.  Every logit row against the plain model."""
+    descriptor carries the decode kernel's work items: the long request is shared among several CTAs per kv head,
+    the short ones take one each.  Every logit row against the plain model."""
     from prism_b200 import ops
     from prism_b200.engine.runner import ModelRunner
     from prism_b200.weights.loader import load_model_folder
@@ -197,9 +197,10 @@ def test_requests_of_unequal_length_decode_together(folder_and_plain, graphs, mo
     seen = []
     real = ops.attention_decode_bf16
 
-    def spy(q, out, k, v, bt, pos, seg, npg, window, scale, nsplit, po, pml, err, plan=None):
-        seen.append((q.shape[0], window, nsplit, None if plan is None else int(plan.item()) if not graphs else -1))
-        return real(q, out, k, v, bt, pos, seg, npg, window, scale, nsplit, po, pml, err, plan=plan)
+    def spy(q, out, k, v, bt, pos, seg, npg, window, scale, nsplit, po, pml, err, items=None, starts=None):
+        seen.append((q.shape[0], window, nsplit, None if items is None else items.shape[0],
+                     None if starts is None or graphs else starts.tolist()))
+        return real(q, out, k, v, bt, pos, seg, npg, window, scale, nsplit, po, pml, err, items=items, starts=starts)
     monkeypatch.setattr(ops, "attention_decode_bf16", spy)
     cfg, t = P.load_folder(folder, device="cuda:0")
     seqs = {"long": random_tokens(8192, 1500, 31), "tiny": random_tokens(8192, 40, 32),
@@ -219,11 +220,15 @@ def test_requests_of_unequal_length_decode_together(folder_and_plain, graphs, mo
                          use_cuda_graph=graphs, graph_batch_sizes=(1, 4))
     got = run_trace(runner, steps)
     full = [s for s in seen if s[0] == 4 and s[1] is None]       # the layers that keep every key
-    assert full and all(ns == 8 and plan is not None for _, _, ns, plan in full), full[:4]
-    if not graphs:
-        want = ops.decode_split_target([1494, 34, 594, 124], 4, None)
-        assert full[0][3] == want and [ops.decode_used_splits(ops.decode_tiles(p, None), want, 8)
-                                       for p in (1494, 34, 594, 124)] == [8, 1, 3, 1]
+    assert full and all(n is not None for _, _, _, n, _ in full), full[:4]
+    if graphs:
+        nkv = json.load(open(os.path.join(folder, "config.json")))["num_key_value_heads"]
+        assert all(n == 2 * ops.num_sms() // nkv for _, _, _, n, _ in full)   # one wave of places per kv head
+    else:
+        # 1,494 + 34 + 594 + 124 keys: 24, 1, 10 and 2 tiles, at three tiles a CTA at least
+        for _, _, ns, n, st in full[:2]:
+            assert ns == 8 and n == 13 and [v >> 16 for v in st] == [8, 1, 3, 1], full[:2]
+            assert sorted(v & 0xffff for v in st) == [0, 3, 11, 12]          # the longest CTAs (4 tiles each) first
     for rid, seq in seqs.items():
         for pos in range(len(seq) - tail - 1, len(seq)):
             err = float((got[(rid, pos)] - ref[rid][pos]).abs().max())

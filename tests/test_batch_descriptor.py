@@ -14,8 +14,12 @@ def test_layout_offsets_are_aligned_and_disjoint():
             assert o % 4 == 0 and o + n <= o2                  # 4 int32 = 16 bytes; no overlap
         assert spans[-1][0] + spans[-1][1] <= lay.total
         assert set(lay.off) == {"token_ids", "positions", "tok_seg", "seg_start", "cached_len", "q_len",
-                                "state_slots", "logit_rows", "decode_plan"} | {f"bt{g}" for g in groups}
-        assert lay.off["decode_plan"][1] == len(groups)
+                                "state_slots", "logit_rows"} | {f"bt{g}" for g in groups}
+    lay = BatchLayout(7, 3, 2, 5, [0, 2], {0: 9, 2: 3})
+    spans = sorted(lay.off.values())
+    for (o, n), (o2, _) in zip(spans, spans[1:]):
+        assert o % 4 == 0 and o + n <= o2
+    assert lay.off["items0"][1] == 36 and lay.off["items2"][1] == 12 and lay.off["starts0"][1] == 3
 
 
 def test_pack_and_views():
@@ -33,11 +37,18 @@ def test_pack_and_views():
     assert ctx.state_slots.tolist() == [2, 0] and ctx.logit_rows.tolist() == [0, 3]
     assert ctx.block_tables[0].tolist() == [[5, 2, 7, 40], [3, 1, 40, 40]]
     assert ctx.block_tables[1].tolist() == [[41, 41, 6, 41], [0, 41, 41, 41]]
-    assert ctx.decode_plan[0].tolist() == [0] and ctx.decode_plan[1].tolist() == [0] and ctx.split_caps == {}
-    planned = pack_batch(lay, tok, pos, seg_of, [0, 1, 4], [9, 4], [1, 3], [2, 0], [0, 3], rows, {0: 40, 1: 41},
-                         decode_plan={1: 77})
-    ctx2 = StepContext(lay, planned, torch.float32, "cpu", None, 64, None, 3, 10)
-    assert ctx2.decode_plan[0].tolist() == [0] and ctx2.decode_plan[1].tolist() == [77]
+    assert ctx.decode_work == {}
+    # the decode kernel's work items of the leading single-token segment, for group 1; a layout with more places
+    # than items marks the rest unused, and the segments after the decoding ones have no items
+    import numpy as np
+    lay2 = BatchLayout(4, 2, 2, 4, [0, 1], {1: 3})
+    items = np.array([[0, 0 | 2 << 16, 9, 0], [0, 1 | 2 << 16, 9, 0]], dtype=np.int32)
+    planned = pack_batch(lay2, tok, pos, seg_of, [0, 1, 4], [9, 4], [1, 3], [2, 0], [0, 3], rows, {0: 40, 1: 41},
+                         {1: (items, np.array([0 | 2 << 16], dtype=np.int32))})
+    ctx2 = StepContext(lay2, planned, torch.float32, "cpu", None, 64, None, 3, 10)
+    got_items, got_starts = ctx2.decode_work[1][:2]
+    assert got_items.tolist() == items.tolist() + [[-1] * 4] and got_starts.tolist() == [2 << 16, 0]
+    assert lay2.off["items1"][0] % 4 == 0 and ctx2.block_tables[1].tolist() == ctx.block_tables[1].tolist()
     # a pure decode step is recognised by its longest segment
     assert StepContext(lay, host, torch.float32, "cpu", None, 64, None, 1, 10).decode_only
 

@@ -3,6 +3,8 @@ host-side choices of ``prism_b200.ops``, which need no GPU."""
 
 import random
 
+import numpy as np
+
 import pytest
 
 from prism_b200 import ops
@@ -119,3 +121,45 @@ def test_decode_plan_shares_a_ragged_batch_by_context():
     assert ops.decode_tiles(40000, 128) <= 3 and ops.decode_tiles(10, 128) == 1 and ops.decode_tiles(64, None) == 2
     # a descriptor without a plan holds 0: the least number of tiles per CTA decides
     assert ops.decode_used_splits(33, 0, 64) == 11 and ops.decode_used_splits(33, 0, 4) == 4
+
+
+def test_decode_work_items_cover_every_request_once():
+    """The items of a step: consecutive per request, split numbers 0 .. used - 1, no CTA without a tile, and the
+    counts that ``decode_plan_for`` gives (less where fewer CTAs leave each the same number of tiles)."""
+    rng = random.Random(5)
+    for _ in range(100):
+        batch = rng.choice([1, 3, 8, 33, 64])
+        nkv = rng.choice([1, 4, 8])
+        window = rng.choice([None, 200, 5000])
+        pos = [rng.choice([0, 63, 64, 900, 7000, 33000]) + rng.randrange(64) for _ in range(batch)]
+        items, starts, most = ops.decode_work_items(pos, nkv, window, sms=148)
+        target, cap = ops.decode_plan_for(pos, nkv, window, sms=148)
+        used_of, first_of = starts >> 16, starts & 0xffff
+        assert items.dtype.name == starts.dtype.name == "int32" and items.shape == (used_of.sum(), 4)
+        assert len(starts) == batch and sorted(first_of.tolist()) == (np.cumsum(sorted_used(items, batch)) - sorted_used(items, batch)).tolist()
+        longest = []
+        for b, p in enumerate(pos):
+            mine = items[first_of[b]:first_of[b] + used_of[b]]
+            used = len(mine)
+            tiles = ops.decode_tiles(p, window)
+            assert 1 <= used <= ops.decode_used_splits(tiles, target, cap) and used <= most
+            assert mine[:, 0].tolist() == [b] * used and mine[:, 3].tolist() == [b] * used
+            assert mine[:, 2].tolist() == [p] * used
+            assert (mine[:, 1] & 0xffff).tolist() == list(range(used)) and (mine[:, 1] >> 16).tolist() == [used] * used
+            per = -(-tiles // used)
+            assert (used - 1) * per < tiles                   # the last CTA has a tile
+            assert -(-tiles // ops.decode_used_splits(tiles, target, cap)) == per     # and none has more than planned
+            longest.append((first_of[b], per))
+        assert most == used_of.max()
+        in_order = [per for _, per in sorted(longest)]
+        assert in_order == sorted(in_order, reverse=True)     # the longest CTAs come first
+
+
+def sorted_used(items, batch):
+    """The requests' item counts in the order in which their items lie."""
+    seen, out = set(), []
+    for tok, word in zip(items[:, 0].tolist(), items[:, 1].tolist()):
+        if tok not in seen:
+            seen.add(tok)
+            out.append(word >> 16)
+    return np.array(out)

@@ -519,35 +519,49 @@ def test_attention_decode_bf16(case):
         assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
 
 
+def _work_items(ops, ctxs, nkv, window, sms, places=None):
+    """The host's work items for a step on the device; ``places``: a grid with more places than items."""
+    items, starts, most = ops.decode_work_items(ctxs, nkv, window, sms=sms)
+    if places:
+        import numpy as np
+        items = np.concatenate([items, np.full((places - len(items), 4), -1, dtype=np.int32)])
+    return torch.from_numpy(items).to(DEV), torch.from_numpy(starts).to(DEV), most
+
+
 @pytest.mark.parametrize("case", DECODE_CASES)
-@pytest.mark.parametrize("target_x16", [0, 48, 52, 130, 1000, 1 << 20])
-def test_attention_decode_bf16_under_a_plan(case, target_x16):
-    """With a plan (tiles per CTA, in sixteenths) every request is shared among the CTAs its own length asks
-    for, at most the grid's extent; the partials beyond hold NaN and must not be read.  The host's
-    ``decode_used_splits`` says how many there are."""
+@pytest.mark.parametrize("sms", [1, 6, 40, 148, 2000])
+def test_attention_decode_bf16_on_work_items(case, sms):
+    """With work items every request is shared among the CTAs that the host chose from its own length (here for
+    GPUs of 1 to 2,000 SMs, so from one CTA each to as many as three tiles allow); a grid with places to spare
+    leaves them alone; partial results are NaN beforehand and positions and segments are not read."""
     ops = _ops()
-    nh, nkv, hd, P, window, ctxs, cap = case
+    nh, nkv, hd, P, window, ctxs, _ = case
     c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=22)
-    out = torch.full((c.T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    part_o = torch.full((c.T, nh, cap, hd), float("nan"), device=DEV)
-    part_ml = torch.full((c.T, nh, cap, 2), float("nan"), device=DEV)
-    err, scale = _err(), hd ** -0.5
-    plan = torch.tensor([target_x16], dtype=torch.int32, device=DEV)
+    scale, err = hd ** -0.5, _err()
     ref = ref_paged_attention(c.q, c.k, c.v, c.bt, c.positions, c.tok_seg, window, scale)
-    ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, c.positions, c.tok_seg, c.num_pages, window, scale,
-                              cap, part_o, part_ml, err, plan=plan)
-    assert int(err) == 0 and not torch.isnan(out.float()).any()
-    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
-    for t, n in enumerate(ctxs if cap > 1 else []):    # exactly the planned partials were written (one CTA: none)
-        used = ops.decode_used_splits(ops.decode_tiles(n, window), target_x16, cap)
-        written = (~torch.isnan(part_ml[t, 0, :, 0])).sum().item()
-        assert written == used, (t, n, written, used)
+    junk = torch.full_like(c.positions, 1 << 20)
+    for places in (None, 700):
+        items, starts, most = _work_items(ops, ctxs, nkv, window, sms, places)
+        n = items.shape[0]
+        out = torch.full((c.T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        part_o = torch.full((n, nh, hd), float("nan"), device=DEV)
+        part_ml = torch.full((n, nh, 2), float("nan"), device=DEV)
+        ops.attention_decode_bf16(c.q, out, c.k, c.v, c.bt, junk, junk, c.num_pages, window, scale,
+                                  most, part_o, part_ml, err, items=items, starts=starts)
+        assert int(err) == 0 and not torch.isnan(out.float()).any()
+        assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+        # a request with one item wrote its output itself; the others left one partial per item
+        used = (starts >> 16).tolist()
+        # (a token's slots: [head][split] from its first item on)
+        written = (~torch.isnan(part_ml[:, :, 0])).sum(1).tolist()          # per item row: nh slots
+        want = [nh if tok >= 0 and used[tok] > 1 else 0 for tok in items[:, 0].tolist()]
+        assert written == want and sum(used) == (items[:, 0] >= 0).sum().item(), (used, written)
 
 
-def test_attention_decode_qkv_under_a_plan():
-    """The decode kernel that finishes the projection takes the same plan."""
+def test_attention_decode_qkv_on_work_items():
+    """The decode kernel that finishes the projection takes the same work items."""
     ops = _ops()
-    nh, nkv, hd, P, window, ctxs, cap = 12, 2, 128, 64, None, [1300, 64, 200, 0, 5000], 16
+    nh, nkv, hd, P, window, ctxs = 12, 2, 128, 64, None, [1300, 64, 200, 0, 5000]
     c = PagedCase([(n, 1) for n in ctxs], nh, nkv, hd, P, torch.bfloat16, seed=23)
     T, ks, D = c.T, 2, (nh + 2 * nkv) * hd
     parts = _rand((ks, T, D), torch.float32, 62, scale=0.5)
@@ -556,18 +570,25 @@ def test_attention_decode_qkv_under_a_plan():
     ops.rope_table(c.positions, inv, table)
     scale, err = hd ** -0.5, _err()
     outs = []
-    for plan in (None, torch.tensor([ops.decode_split_target(ctxs, nkv, window, sms=20)], dtype=torch.int32, device=DEV)):
+    for planned in (False, True):
         k, v = c.k.clone(), c.v.clone()
         got = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-        po = torch.full((T, nh, cap, hd), float("nan"), device=DEV)
-        pml = torch.full((T, nh, cap, 2), float("nan"), device=DEV)
+        if planned:
+            items, starts, most = _work_items(ops, ctxs, nkv, window, 20, places=64)
+            assert most > 1 and (starts >> 16).sum().item() > T
+            po = torch.full((items.shape[0], nh, hd), float("nan"), device=DEV)
+            pml = torch.full((items.shape[0], nh, 2), float("nan"), device=DEV)
+        else:
+            items, starts, most = None, None, 16
+            po = torch.full((T, nh, most, hd), float("nan"), device=DEV)
+            pml = torch.full((T, nh, most, 2), float("nan"), device=DEV)
         ops.attention_decode_qkv_bf16(parts, None, table, 1 << 20, got, k, v, c.bt, c.positions, c.tok_seg, c.num_pages,
-                                      nh, window, scale, cap, po, pml, err, plan=plan)
+                                      nh, window, scale, most, po, pml, err, items=items, starts=starts)
         assert int(err) == 0 and not torch.isnan(got.float()).any()
-        outs.append(got.float())
-        if plan is not None:
-            assert sorted((~torch.isnan(pml[:, 0, :, 0])).sum(1).tolist()) != [cap] * T      # the plan was followed
-    assert torch.allclose(outs[0], outs[1], atol=4e-3, rtol=1e-2)
+        outs.append((got.float(), k, v))
+    assert torch.allclose(outs[0][0], outs[1][0], atol=4e-3, rtol=1e-2)
+    for a, b in ((outs[0][1], outs[1][1]), (outs[0][2], outs[1][2])):       # the tokens' own keys and values were stored
+        assert torch.equal(torch.isnan(a), torch.isnan(b)) and torch.equal(a.nan_to_num(), b.nan_to_num())
 
 
 @pytest.mark.parametrize("case", DECODE_CASES + [(8, 2, 64, 16, 40, [100, 39, 40, 41, 0], 3)])     # head sizes 16 .. 128
