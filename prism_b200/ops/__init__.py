@@ -771,9 +771,9 @@ def decode_tiles(position: int, window: Optional[int]) -> int:
 
 
 def decode_used_splits(tiles: int, target_x16: int, cap: int) -> int:
-    """CTAs that share one request's keys under a plan: as many as keep each at or below the target, none with
-    fewer than ``DECODE_MIN_TILES`` tiles, at most ``cap`` (csrc/attention_bf16.cuh computes the same)."""
-    target = max(target_x16, DECODE_MIN_TILES * 16)              # a descriptor without a plan holds 0
+    """CTAs that share one request's keys under a target of ``target_x16 / 16`` tiles per CTA: as many as keep
+    each at or below the target, none with fewer than ``DECODE_MIN_TILES`` tiles, at most ``cap``."""
+    target = max(target_x16, DECODE_MIN_TILES * 16)
     return min(max(min(-(-tiles * 16 // target), tiles // DECODE_MIN_TILES), 1), cap)
 
 
