@@ -52,7 +52,7 @@ def main():
     prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
     sp = SamplingParams(max_new_tokens=new, ignore_eos=True)
     # capture the decode graphs of every bucket before the timed run, as a server does when it starts
-    eng.runner.warmup_graphs()
+    eng.warmup()
     eng.generate([p[:16] for p in prompts[:4]], SamplingParams(max_new_tokens=3, ignore_eos=True))
     steps0, pre0 = eng.stats.steps, eng.stats.preemptions
     torch.cuda.synchronize()

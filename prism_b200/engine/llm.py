@@ -88,6 +88,12 @@ class Engine:
         return [GenerationResult(r.generated_tokens, r.finish_reason, r.ttft, r.tbt, r.num_preemptions, r.error)
                 for r in reqs]
 
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None) -> None:
+        """Capture the decode graphs before the first request (engine/executor.py:312-318 does it for a list of
+        batch sizes): every bucket's graphs up to ``max_num_seqs``, or those of ``batch_sizes``.  Without it each
+        graph is captured at its first use, which that step pays for (tens of milliseconds)."""
+        self.runner.warmup_graphs(batch_sizes)
+
     @property
     def stats(self):
         return self.scheduler.stats

@@ -72,7 +72,8 @@ class ModelRunner:
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]
         from .. import ops
         self._sms = ops.num_sms(self.device)
-        self._graphs: Dict[tuple, dict] = {}     # (bucket, decode grid extents) -> captured step
+        self._graphs: Dict[tuple, dict] = {}     # (bucket, decode attention places, merge kernels) -> captured step
+        self._work_memo: Dict[int, dict] = {}    # per cache group: the last step's decode work items
         self.graph_kernel_launches = 0       # kernels of this library replayed inside graphs
         self.last_h2d_bytes = 0              # bytes of the last step's batch descriptor (host to device)
 
@@ -171,7 +172,8 @@ class ModelRunner:
         work = {}
         for g in self.paged_groups:
             need = self.groups[g].need
-            work[g] = ops.decode_work_items(cached[:lead], need.num_kv_heads, need.window, self._sms, n_real)
+            work[g] = ops.decode_work_items(cached[:lead], need.num_kv_heads, need.window, self._sms, n_real,
+                                            self._work_memo.setdefault(g, {}))
         return work
 
     # ---- decode graphs ---------------------------------------------------------------

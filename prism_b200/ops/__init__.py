@@ -888,16 +888,27 @@ def decode_plan_for(positions, nkv: int, window: Optional[int], sms: Optional[in
 
 
 def decode_work_items(positions, nkv: int, window: Optional[int], sms: Optional[int] = None,
-                      n_real: Optional[int] = None):
+                      n_real: Optional[int] = None, memo: Optional[dict] = None):
     """The decode attention kernel's work for a step: ``(items [n, 4], starts [B], most)`` as int32 arrays
     and the most items any request has.  Request b (at ``positions[b]``, token and segment b of the step) gets
     ``decode_plan_for``'s number of CTAs per kv head, less where fewer already leave each the same number of
     tiles: ``used`` items ``{b, split | used << 16, position, b}`` from item ``first`` on, ``starts[b] = first |
     used << 16``.  The requests whose CTAs are longest come first, so that when the items are more than fit on
-    the GPU at once the short ones run last.  ``n_real``: the requests after these are a graph bucket's padding."""
-    target, cap = decode_plan_for(positions, nkv, window, sms, n_real)
+    the GPU at once the short ones run last.  ``n_real``: the requests after these are a graph bucket's padding.
+    ``memo``: a dict the caller keeps between steps; the items depend on the positions only through the
+    requests' tile counts, which change once in 64 steps, so the step before has usually left all but the
+    position column."""
     pos = np.asarray(positions, dtype=np.int64)
     tiles = _tiles_of(pos, window)
+    key = None
+    if memo is not None:
+        key = (tiles.tobytes(), n_real, nkv, window, sms)
+        if memo.get("key") == key:
+            items, tok, starts, most = memo["value"]
+            items = items.copy()
+            items[:, 2] = pos[tok]
+            return items, starts, most
+    target, cap = decode_plan_for(positions, nkv, window, sms, n_real)
     used = _used_splits(tiles, target, cap)
     per = -(-tiles // used)
     used = -(-tiles // per)                                # no CTA without a tile
@@ -907,7 +918,10 @@ def decode_work_items(positions, nkv: int, window: Optional[int], sms: Optional[
     tok = np.repeat(order, used[order])
     split = np.arange(len(tok)) - first[tok]
     items = np.stack([tok, split | (used[tok] << 16), pos[tok], tok], axis=1).astype(np.int32)
-    return items, (first | (used << 16)).astype(np.int32), int(used.max())
+    starts, most = (first | (used << 16)).astype(np.int32), int(used.max())
+    if memo is not None:
+        memo["key"], memo["value"] = key, (items, tok, starts, most)
+    return items, starts, most
 
 
 DECODE_MIN_TILES = 3                # 64-key tiles a split CTA keeps at least (csrc/attention_bf16.cuh: DEC_MIN_TILES)

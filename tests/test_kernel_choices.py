@@ -163,3 +163,20 @@ def sorted_used(items, batch):
             seen.add(tok)
             out.append(word >> 16)
     return np.array(out)
+
+
+def test_decode_work_items_remembered_between_steps_are_the_same():
+    """The caller's memo saves the planning while no request's tile count changes; the result is the same."""
+    rng = random.Random(9)
+    for _ in range(10):
+        batch, window = rng.choice([1, 5, 33]), rng.choice([None, 300])
+        start = [rng.randint(0, 5000) for _ in range(batch)]
+        memo, reused = {}, 0
+        for step in range(150):
+            pos = [p + step for p in start]
+            before = memo.get("key")
+            a = ops.decode_work_items(pos, 4, window, sms=148, memo=memo)
+            reused += memo.get("key") == before
+            b = ops.decode_work_items(pos, 4, window, sms=148)
+            assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]) and a[2] == b[2]
+        assert batch > 1 or reused >= 140
