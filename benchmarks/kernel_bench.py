@@ -3,7 +3,7 @@ flushing L2 between timed launches, and prints achieved bandwidth or FLOP/s.
 
     python benchmarks/kernel_bench.py gemv  [--m 8]
     python benchmarks/kernel_bench.py gemm_tc [--m 8]
-    python benchmarks/kernel_bench.py attn_decode [--batch 8 --ctx 4096]
+    python benchmarks/kernel_bench.py attn_decode [--batch 8 --ctx 4096] [--ragged] [--splits N]
     python benchmarks/kernel_bench.py attn_prefill [--tokens 2048] [--mma-sync]
     python benchmarks/kernel_bench.py small [--m 8]       (norm, rope, swiglu, embed, sample)
 
@@ -108,20 +108,34 @@ def paged_case(batch, ctx, q_len, page=256):
 def bench_attn_decode(args):
     B, ctx = args.batch, args.ctx
     kc, vc, bt, q, pos, seg, _, _, n_pages = paged_case(B, ctx - 1, 1)
+    if args.ragged:
+        g = torch.Generator().manual_seed(0)
+        pos = torch.randint(ctx // 32, ctx, (B,), generator=g).to(torch.int32).to(DEV)
+        pos[0] = ctx - 1
     out = torch.empty(B, NH * HD, device=DEV, dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ns = args.splits or ops.decode_splits(B, NKV, args.bound or ctx, None)
-    po = torch.empty(B, NH, ns, HD, device=DEV)
-    pml = torch.empty(B, NH, ns, 2, device=DEV)
-    fn = lambda: ops.attention_decode_bf16(q, out, kc, vc, bt, pos, seg, n_pages, None, HD ** -0.5, ns, po, pml, err)
+    if args.splits or args.bound:
+        # equal splits for every request, as a caller without work items gets them
+        ns = args.splits or ops.decode_splits(B, NKV, args.bound or ctx, None)
+        po = torch.empty(B, NH, ns, HD, device=DEV)
+        pml = torch.empty(B, NH, ns, 2, device=DEV)
+        fn = lambda: ops.attention_decode_bf16(q, out, kc, vc, bt, pos, seg, n_pages, None, HD ** -0.5, ns, po, pml, err)
+    else:
+        # the engine's way: work items from the requests' contexts (--ragged: contexts from ctx/32 to ctx)
+        items, starts, ns = ops.decode_work_items(pos.tolist(), NKV, None)
+        items, starts = torch.from_numpy(items).to(DEV), torch.from_numpy(starts).to(DEV)
+        po = torch.empty(items.shape[0], NH, HD, device=DEV)
+        pml = torch.empty(items.shape[0], NH, 2, device=DEV)
+        fn = lambda: ops.attention_decode_bf16(q, out, kc, vc, bt, pos, seg, n_pages, None, HD ** -0.5, ns, po, pml, err,
+                                               items=items, starts=starts)
     if args.once:
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
         return
     t = timeit(fn)
-    gb = B * ctx * NKV * HD * 2 * 2 / 1e9
-    print(f"attn_decode B={B} ctx={ctx} splits={ns}: {t:8.1f} us  {gb / t * 1e6:7.0f} GB/s of K/V")
+    gb = int(pos.sum() + B) * NKV * HD * 2 * 2 / 1e9
+    print(f"attn_decode B={B} ctx={'<=' if args.ragged else ''}{ctx} splits<={ns}: {t:8.1f} us  {gb / t * 1e6:7.0f} GB/s of K/V")
 
 
 def bench_attn_prefill(args):
@@ -178,6 +192,7 @@ if __name__ == "__main__":
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--bound", type=int, default=0, help="context bound used to choose the splits")
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: CTAs per (token, kv head); attn_prefill: CTAs that share a query tile's keys; 0 = the engine's choice")
+    ap.add_argument("--ragged", action="store_true", help="attn_decode: contexts drawn from ctx/32 .. ctx, one of them ctx")
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--cached", type=int, default=0, help="attn_prefill: tokens already in the cache before the portion")
     ap.add_argument("--mma-sync", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
