@@ -865,15 +865,29 @@ def decode_split_target(positions, nkv: int, window: Optional[int], sms: Optiona
 def decode_plan_for(positions, nkv: int, window: Optional[int], sms: Optional[int] = None,
                     n_real: Optional[int] = None):
     """``(target_x16, cap)`` for a step's decoding requests: the plan and the most CTAs any request gets under
-    it.  A large batch whose long, equal contexts leave one CTA per (token, kv head) and the GPU unevenly
-    filled (256 CTAs are two on 108 SMs and one on 40) gets the few equal splits that even it out
-    (``DECODE_BALANCE_FROM_TILES``; batch 64 at 32,768 keys: 717 -> 673 us)."""
+    it.  Many requests (a third of a wave of CTAs or more) with long contexts of about one length
+    (``DECODE_LONG_FROM_TILES``) get equal splits chosen by how they fill whole waves, see below; the older
+    rule for one CTA each at 16,384 keys and more (``DECODE_BALANCE_FROM_TILES``) remains for what that leaves."""
     n_sms = sms or num_sms()
     target = decode_split_target(positions, nkv, window, n_sms, n_real)
     tiles = _tiles_of(positions, window)
     cap = int(_used_splits(tiles, target).max())
-    least = int(tiles.min())
-    if cap == 1 and least >= DECODE_BALANCE_FROM_TILES:
+    real = tiles if n_real is None else tiles[:n_real]
+    least, most = int(real.min()), int(real.max())
+    slots = 2 * n_sms
+    if least >= DECODE_LONG_FROM_TILES and 4 * least >= 3 * most and 3 * len(tiles) * nkv >= slots:
+        # many requests with long contexts of about one length: all get the same number of CTAs - one that
+        # fills its last wave to 85 % or more, and among those the one that makes about two waves (measured at
+        # 8,192 and 16,384 keys on 4 kv heads: 32 requests best in 4 CTAs each, 40 in 5, 48 in 4 or 3, 64 in 2
+        # or 3; up to 11 % of the kernel's time against one wave's worth)
+        def waves(k):
+            return len(tiles) * nkv * k / slots
+        ks = [k for k in range(1, 9) if k == 1 or least // k >= 16]
+        full = [k for k in ks if waves(k) / -(-waves(k) // 1) >= 0.85]
+        k = min(full, key=lambda k: abs(waves(k) - 2.0)) if full else max(ks, key=lambda k: waves(k) / -(-waves(k) // 1))
+        target = -(-most * 16 // k)
+        cap = int(_used_splits(tiles, target).max())
+    elif cap == 1 and least >= DECODE_BALANCE_FROM_TILES:
         def fill(k):
             m = len(tiles) * nkv * k / n_sms
             return m / -(-m // 1)
@@ -924,6 +938,7 @@ def decode_work_items(positions, nkv: int, window: Optional[int], sms: Optional[
     return items, starts, most
 
 
+DECODE_LONG_FROM_TILES = 128         # 8,192 keys
 DECODE_MIN_TILES = 3                # 64-key tiles a split CTA keeps at least (csrc/attention_bf16.cuh: DEC_MIN_TILES)
 DECODE_BALANCE_FROM_TILES = 256     # 16,384 keys: below, the merge costs what the balance gains (batch 64: 8,192 keys
                                     # 203 -> 201 us in 4 splits, 32,768 keys 717 -> 673 us)

@@ -84,9 +84,12 @@ def test_decode_plan_reproduces_the_measured_choices_for_equal_contexts():
         target, cap = ops.decode_plan_for([2099] * batch, 4, None, sms=148)
         assert cap == want, (batch, cap)
         assert ops.decode_used_splits(ops.decode_tiles(2099, None), target, 64) == want
-    # the few equal splits that even out a large batch against long contexts
-    target, cap = ops.decode_plan_for([32767] * 64, 4, None, sms=148)
-    assert cap == ops.decode_splits(64, 4, 32768, None, sms=148) > 1
+    # many long contexts of one length: the number of CTAs each that fills whole waves, about two of them
+    for batch, want in [(24, 3), (32, 4), (40, 5), (48, 3), (64, 2)]:
+        for keys in (8192, 16384, 32768):
+            assert ops.decode_plan_for([keys - 1] * batch, 4, None, sms=148)[1] == want, (batch, keys)
+    assert ops.decode_plan_for([8191] * 8, 4, None, sms=148)[1] == 9          # a few requests: one wave as before
+    assert ops.decode_plan_for([4095] * 48, 4, None, sms=148)[1] == 1         # shorter contexts: as before
 
 
 def test_decode_plan_shares_a_ragged_batch_by_context():
