@@ -151,9 +151,9 @@ def result_line(args, cfg, layers_model, pk, B, ms, ctx_mean, prefill_ms, points
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         # decode at batch 1 and 64: tokens a second, and beside them the step time and the fraction of the
         # measured copy bandwidth (weights once + the live requests' keys and values over the step time)
-        "points": {k: v["value"] for k, v in points.items()},
-        "points_ms": {k: v["ms"] for k, v in points.items()},
-        "points_frac": {k: v["frac"] for k, v in points.items()},
+        "points": {k: v and v["value"] for k, v in points.items()},
+        "points_ms": {k: v and v["ms"] for k, v in points.items()},
+        "points_frac": {k: v and v["frac"] for k, v in points.items()},
     }
     if impl:
         out["impl"] = impl
@@ -181,7 +181,14 @@ def run(args):
     PROMPT, CONTEXT = args.prompt_len, 2 * args.prompt_len
     B, K, Wm = args.batch, args.steps, args.warmup
     pages_per_seq = CONTEXT // PAGE
-    most = max(64, B)
+    # the cache pool holds the largest batch that is measured: 64 requests for the batch-64 point, unless only
+    # --batch is asked for (--quick) or 64 requests of this context do not fit beside the weights - then the
+    # batch-64 point is left out (null)
+    w_bytes, kv_per_seq, _ = model_bytes_flops(cfg, 1, CONTEXT, PROMPT)
+    room = torch.cuda.mem_get_info(0)[0] - w_bytes - (12 << 30)
+    most = B if args.quick else max(64, B)
+    if most * kv_per_seq > room:
+        most = max(B, min(most, int(room // kv_per_seq)))
     ec = EngineConfig(kv_page_size=PAGE, num_pages=most * pages_per_seq + 8, max_seq_len=CONTEXT, use_cuda_graph=True,
                       graph_batch_sizes=tuple(sorted({1, 8, 64, B})),
                       scheduler=SchedulerConfig(max_batch_tokens=max(8, B) * PROMPT, max_num_seqs=most,
@@ -276,6 +283,9 @@ def run(args):
     for b in (1, 64):
         if b == B:
             points[f"decode_b{b}"] = point(cfg, pk, b, ms, ctx_mean, PROMPT)
+            continue
+        if b > most:
+            points[f"decode_b{b}"] = None              # that many requests of this context do not fit
             continue
         m, _, c, _ = decode_bench(b, POINT_STEPS, POINT_WARMUP)
         points[f"decode_b{b}"] = point(cfg, pk, b, m, c, PROMPT)
