@@ -38,7 +38,12 @@ SHAPES = {
 }
 PAGE = 256
 POINT_STEPS, POINT_WARMUP = 128, 5        # decode steps timed for each of the other batch sizes
-E2E_MIN_TOKENS = 128                       # new tokens per request of the end-to-end run, at least
+E2E_MIN_TOKENS = 256                       # new tokens per request of the end-to-end run, at least
+# Both arms wait this long between the prompts and the decode steps: for about 75 ms after a burst of prefill
+# GEMMs at the power cap the GPU runs ~10 % slower (batch 8: 3.28 instead of 2.98 ms a step for the first
+# 23 steps; with 0.3 s of rest 2.98 from the second step on), and a short run (--steps 20) would measure that.
+# The end-to-end figure has no such rest: a request's tokens follow its prompt at once.
+SETTLE_S = 0.5
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 # what the reference publishes for this model (docs/benchmarks.md:9-14): one H100, 5-token prompts
 PUBLISHED_H100 = {1: 150.0, 2: 286.0, 4: 564.0, 8: 1096.0, 16: 2133.0, 32: 4000.0}
@@ -131,7 +136,8 @@ def result_line(args, cfg, layers_model, pk, B, ms, ctx_mean, prefill_ms, points
               "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
               "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
               "prompt_len": PROMPT, "page_size": PAGE, "cuda_graph": True,
-              "l2": "inputs larger than L2 (all weights are read every step)", "peaks": pk["source"]}
+              "l2": "inputs larger than L2 (all weights are read every step)", "peaks": pk["source"],
+              "settle_s": SETTLE_S}
     config.update(extra_config or {})
     out = {
         "metric": "decode tok/s (Qwen2.5-%s shape, bf16, batch %d, %d-token prompts)" % (args.model.upper(), B, PROMPT),
@@ -210,6 +216,8 @@ def run(args):
             runner.begin_request(rid)
             runner.step([Segment(rid, p, [])])
         toks = [1] * batch
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)
 
         def one():
             logits = runner.step([Segment(rid, [t], [0]) for rid, t in zip(ids, toks)])
@@ -407,6 +415,8 @@ def _run_reference(args, torch, SimpleNamespace, StaticWeightPool, FlashAttnKVCa
             if batch > 1:
                 ex.warmup_batch_graphs([batch])
             toks = [1] * batch
+            torch.cuda.synchronize()
+            time.sleep(SETTLE_S)
 
             def one():
                 nonlocal toks
