@@ -64,6 +64,24 @@ def test_decode_graphs_give_the_eager_result(name, dtype):
     assert [r.token_ids for r in b2] == [r.token_ids for r in b]
 
 
+def test_warmup_captures_the_decode_graphs_ahead_of_the_first_request():
+    """``Engine.warmup()``: every bucket's graphs (with and without the merge of split contexts) exist before the
+    first request, and generation then captures nothing more and gives the tokens of an engine without graphs."""
+    from prism_b200 import SamplingParams
+    vocab = TINY["D"][0]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 170 + n) for n in (3, 90, 260)]
+    sp = [SamplingParams(max_new_tokens=n) for n in (9, 12, 7)]
+    eg = engine("D", "bfloat16", graph=True)
+    eg.warmup()
+    buckets = set(eg.runner.graph_batch_sizes)
+    assert {key[0] for key in eg.runner._graphs} == buckets and len(eg.runner._graphs) == 2 * len(buckets)
+    before = set(eg.runner._graphs)
+    got = eg.generate(prompts, sp)
+    assert set(eg.runner._graphs) == before and eg.runner.graph_kernel_launches > 0
+    want = engine("D", "bfloat16", graph=False).generate(prompts, sp)
+    assert [r.token_ids for r in got] == [r.token_ids for r in want]
+
+
 def test_temperature_sampling_matches_the_plain_sampler():
     """Config B's workload: prompts 1/9/40/71, prefill in portions of 16 mixed with
     decode, 6 tokens at temperature 0.7 from seed 4 - the same draws as the plain
